@@ -1,0 +1,63 @@
+"""Generates tests/golden/*.npz from the reference's own CPU kernels.
+
+Runs only where the reference checkout and oracle/_ref exist (build them with
+`python oracle/build_ref.py`).  For every case in tests/synth.py:GOLDEN_CASES
+the flow is the decode step the reference performs: all but the last token of
+every sequence are written with the reference's CPU reshape_and_cache
+(GLakeServe/csrc/cpu/cache.cpp:103-128), the last token is appended by a second
+call, then paged_attention_v1 / _v2 (GLakeServe/csrc/cpu/attention.cpp:415-430,
+:730-746) produce the outputs that are stored.  Stored per case: output bits
+(uint16 view of bf16), context lengths, a sha256 of the inputs, and a sha256 of
+the cache contents gathered back to [token, kv_head, d] order.
+
+Usage: python tests/golden/make_golden.py
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+from oracle import oracle as O  # noqa: E402
+from tests import synth  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def run_case(name):
+    seed, lens, h, kvh = synth.golden_lens(name)
+    q, k, v = synth.make_case(seed, lens, h, kvh)
+    ref = O.load_ref("bf16")
+    assert ref is not None, "build oracle/_ref first (python oracle/build_ref.py)"
+    # prefill all but the last token, then append the last one (decode step)
+    # Blocks are sized for L tokens with the last row zeroed; token L-1 then goes
+    # through the reference kernel in a second call.
+    cache = O.RefPagedCache(ref, [torch.cat([x[:-1], torch.zeros_like(x[-1:])]) for x in k],
+                            [torch.cat([x[:-1], torch.zeros_like(x[-1:])]) for x in v])
+    last_slots = torch.tensor(
+        [int(cache.block_tables[i, (n - 1) // O.REF_BLOCK]) * O.REF_BLOCK + (n - 1) % O.REF_BLOCK
+         for i, n in enumerate(lens)], dtype=torch.int64)
+    cache.append(torch.stack([x[-1] for x in k]), torch.stack([x[-1] for x in v]), last_slots)
+    gathered = [cache.gather(i) for i in range(len(lens))]
+    for i in range(len(lens)):
+        assert torch.equal(gathered[i][0], k[i]) and torch.equal(gathered[i][1], v[i])
+    scale = 128 ** -0.5
+    out = cache.attend(q, scale)
+    np.savez_compressed(
+        os.path.join(HERE, name + ".npz"),
+        out_bits=out.view(torch.uint16).numpy(),
+        lens=np.asarray(lens, dtype=np.int32),
+        shape=np.asarray([len(lens), h, kvh, 128], dtype=np.int32),
+        seed=np.asarray(seed),
+        input_sha256=np.asarray(synth.digest(q, k, v)),
+        cache_sha256=np.asarray(synth.digest([g[0] for g in gathered], [g[1] for g in gathered])),
+        kernel=np.asarray("v2" if max(lens) > 8192 else "v1"),
+    )
+    print(name, "lens", lens[:8], "out", tuple(out.shape), "max|out|", float(out.float().abs().max()))
+
+
+if __name__ == "__main__":
+    for name in synth.GOLDEN_CASES:
+        run_case(name)

@@ -1,0 +1,55 @@
+"""Deterministic synthetic inputs for the parity tests and the golden fixtures.
+
+numpy's legacy RandomState stream is frozen across numpy versions, so a seed
+identifies the inputs for good; fixtures therefore store outputs plus a digest
+of the inputs instead of the inputs themselves.
+"""
+import hashlib
+
+import numpy as np
+import torch
+
+
+def normal_bf16(rs, *shape):
+    return torch.from_numpy(rs.standard_normal(shape).astype(np.float32)).bfloat16()
+
+
+def make_case(seed, lens, h, kvh, d=128):
+    """Q [B,H,D]; per-sequence K, V [L_i, KVH, D]; all ~N(0,1) rounded to bf16.
+    lens are context lengths INCLUDING the token appended in the decode step."""
+    rs = np.random.RandomState(seed)
+    q = normal_bf16(rs, len(lens), h, d)
+    k = [normal_bf16(rs, n, kvh, d) for n in lens]
+    v = [normal_bf16(rs, n, kvh, d) for n in lens]
+    return q, k, v
+
+
+def uniform_lens(seed, batch, lo, hi):
+    rs = np.random.RandomState(seed + 7919)
+    return [int(x) for x in rs.randint(lo, hi + 1, size=batch)]
+
+
+def digest(*tensors):
+    m = hashlib.sha256()
+    for t in tensors:
+        for x in (t if isinstance(t, (list, tuple)) else [t]):
+            m.update(x.contiguous().view(torch.uint8).numpy().tobytes())
+    return m.hexdigest()
+
+
+# name -> (seed, lens or ("uniform", batch, lo, hi), H, KVH)
+GOLDEN_CASES = {
+    "gqa4_small": (1, [37, 512, 100, 16], 8, 2),
+    "mha_edges": (2, [1, 2, 255, 256, 257], 4, 4),
+    "mha_chunk_cross": (3, [1023, 1024, 1025], 8, 8),
+    "gqa8": (4, [300, 2049, 64], 16, 2),
+    "long_partitioned": (5, [9000, 8193], 8, 1),
+    "config1_op": (0, ("uniform", 8, 512, 2048), 32, 32),
+}
+
+
+def golden_lens(name):
+    seed, lens, h, kvh = GOLDEN_CASES[name]
+    if isinstance(lens, tuple):
+        lens = uniform_lens(seed, *lens[1:])
+    return seed, lens, h, kvh
