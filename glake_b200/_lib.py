@@ -1,0 +1,95 @@
+"""ctypes binding of libvtensor.so (the C ABI declared in include/vtensor.h).
+
+There is no fallback: if the shared library is missing the import raises, and
+every non-zero status from the library becomes a VTensorError.
+"""
+import ctypes
+import os
+from ctypes import POINTER, c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_uint64, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libvtensor.so")
+
+VT_OK = 0
+VT_ERR_INVALID, VT_ERR_DRIVER, VT_ERR_POOL_EMPTY, VT_ERR_RESERVE, VT_ERR_TIMEOUT = 1, 2, 3, 4, 5
+VT_ERR_UNSUPPORTED, VT_ERR_CUDA, VT_ERR_STATE, VT_ERR_NO_DRIVER, VT_ERR_KERNEL = 6, 7, 8, 9, 10
+VT_KV_BF16, VT_KV_FP8_E4M3 = 0, 1
+
+
+class VTensorError(RuntimeError):
+    def __init__(self, status, where=""):
+        self.status = status
+        drv = lib.vt_last_driver_error() if status == VT_ERR_DRIVER else 0
+        msg = lib.vt_strerror(status).decode()
+        super().__init__(f"{where}: {msg} (status {status}" + (f", CUresult {drv})" if drv else ")"))
+
+
+class Stats(ctypes.Structure):
+    _fields_ = [(n, c_uint64) for n in (
+        "chunks_total", "chunks_free", "chunk_bytes", "map_calls", "unmap_calls", "set_access_calls",
+        "map_ns", "async_requests", "async_completed", "async_failed", "segments")]
+
+
+def _load():
+    if not os.path.isfile(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `make -C {os.path.join(_HERE, 'csrc')}` "
+            "(or __graft_entry__.build()); glake_b200 has no CPU or PyTorch fallback")
+    L = ctypes.CDLL(LIB_PATH)
+    vp, sz = c_void_p, c_size_t
+    sigs = {
+        "vt_strerror": (c_char_p, [c_int]),
+        "vt_version": (c_char_p, []),
+        "vt_last_driver_error": (c_int, []),
+        "vt_use_mock_driver": (c_int, [c_int]),
+        "vt_mock_fail_nth": (c_int, [c_char_p, c_int]),
+        "vt_mock_map_delay_us": (c_int, [c_int]),
+        "vt_pool_create": (c_int, [c_int, sz, sz, POINTER(vp)]),
+        "vt_pool_destroy": (c_int, [vp]),
+        "vt_pool_free_chunks": (c_int, [vp, POINTER(sz)]),
+        "vt_pool_stats": (c_int, [vp, POINTER(Stats)]),
+        "vt_seg_create": (c_int, [vp, c_int, sz, sz, POINTER(vp)]),
+        "vt_seg_destroy": (c_int, [vp]),
+        "vt_seg_k_ptr": (c_int, [vp, c_int, POINTER(c_uint64)]),
+        "vt_seg_v_ptr": (c_int, [vp, c_int, POINTER(c_uint64)]),
+        "vt_seg_used": (c_int, [vp, POINTER(sz)]),
+        "vt_seg_set_used": (c_int, [vp, sz]),
+        "vt_seg_mapped": (c_int, [vp, POINTER(sz)]),
+        "vt_seg_reserved": (c_int, [vp, POINTER(sz)]),
+        "vt_seg_grow": (c_int, [vp, sz]),
+        "vt_seg_grow_async": (c_int, [vp, c_int]),
+        "vt_seg_ready": (c_int, [vp, POINTER(c_int)]),
+        "vt_seg_wait": (c_int, [vp, c_uint64]),
+        "vt_seg_release": (c_int, [vp, sz]),
+        "vt_extend_batch": (c_int, [POINTER(vp), c_int, POINTER(c_int64), POINTER(c_uint64), c_uint64, c_int,
+                                    c_uint64, POINTER(c_int64)]),
+        "vt_table_create": (c_int, [vp, c_int, POINTER(vp)]),
+        "vt_table_destroy": (c_int, [vp]),
+        "vt_table_set": (c_int, [vp, c_int, c_uint64]),
+        "vt_table_fill": (c_int, [vp, vp, POINTER(vp), c_int, c_int]),
+        "vt_table_dptr": (c_int, [vp, POINTER(c_uint64)]),
+        "vt_pool_read": (c_int, [vp, vp, c_uint64, sz]),
+        "vt_pool_write": (c_int, [vp, c_uint64, vp, sz]),
+        "vt_append": (c_int, [vp, vp, c_int64, c_int64, vp, vp, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
+                              vp, vp, vp]),
+        "vt_kv_scales": (c_int, [vp, c_int64, c_int, c_int, c_int, vp, vp]),
+        "vt_decode_attn_workspace_bytes": (c_int, [c_int, c_int, c_int, c_int, POINTER(sz)]),
+        "vt_decode_attn": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
+                                   c_float, c_int, vp, vp, vp, vp, sz, c_int, vp]),
+        "vt_decode_attn_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int),
+                                        POINTER(c_int)]),
+        "vt_decode_attn_status": (c_int, [vp, vp, POINTER(c_int)]),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(L, name)  # AttributeError here means the .so is stale: rebuild
+        fn.restype, fn.argtypes = res, args
+    L._vt_symbols = tuple(sigs)
+    return L
+
+
+lib = _load()
+
+
+def check(status, where=""):
+    if status != VT_OK:
+        raise VTensorError(status, where)

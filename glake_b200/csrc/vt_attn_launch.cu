@@ -1,0 +1,201 @@
+// Split-K planning, the partial-result merge kernel, and the C entry points of
+// the device-side path.
+#include <algorithm>
+
+#include "../../include/vtensor.h"
+#include "vt_device.cuh"
+#include "vt_kernels.h"
+
+namespace vt {
+namespace {
+
+constexpr int kMinPartTokens = 256;
+constexpr size_t kStatusBytes = 256;
+
+// Merges the per-partition partials of one (sequence, q head):
+//   out = sum_p 2^(m_p - M) * o_p / sum_p 2^(m_p - M) * l_p,  M = max_p m_p.
+// Sequences that fit one partition were finalised by the attention kernel.
+template <bool FP8>
+__global__ void __launch_bounds__(kHeadDim) attn_reduce_kernel(AttnParams p) {
+  const int hq = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
+  const int seq_len = p.seq_lens[b];
+  const int n_parts = (seq_len + p.part_tokens - 1) / p.part_tokens;
+  if (n_parts <= 1) return;
+  const size_t base = (static_cast<size_t>(b) * p.h + hq) * p.max_parts;
+  float M = -INFINITY;
+  for (int i = 0; i < n_parts; ++i) M = fmaxf(M, p.ws_ml[(base + i) * 2]);
+  float L = 0.f, O = 0.f;
+  for (int i = 0; i < n_parts; ++i) {
+    const float f = exp2f(p.ws_ml[(base + i) * 2] - M);
+    L = fmaf(f, p.ws_ml[(base + i) * 2 + 1], L);
+    O = fmaf(f, p.ws_o[(base + i) * kHeadDim + d], O);
+  }
+  const float vs = FP8 ? p.v_scale[hq / (p.h / p.kvh)] : 1.0f;
+  static_cast<__nv_bfloat16 *>(p.out)[b * p.out_stride + hq * kHeadDim + d] = __float2bfloat16(O / L * vs);
+  if (p.lse && d == 0) p.lse[b * p.h + hq] = (M + log2f(L)) * 0.6931471805599453f;
+}
+
+}  // namespace
+
+size_t attn_workspace_bytes(int batch, int h, int max_parts) {
+  const size_t rows = static_cast<size_t>(batch) * h * max_parts;
+  size_t ml = (rows * 2 * sizeof(float) + 255) / 256 * 256;
+  return kStatusBytes + ml + rows * kHeadDim * sizeof(float);
+}
+
+size_t attn_workspace_bound(int batch, int h, int max_seq_len) {
+  const int parts = std::max(1, (max_seq_len + kMinPartTokens - 1) / kMinPartTokens);
+  return attn_workspace_bytes(batch, h, parts);
+}
+
+void carve_workspace(void *ws, int batch, int h, int max_parts, AttnParams *p) {
+  char *c = static_cast<char *>(ws);
+  const size_t rows = static_cast<size_t>(batch) * h * max_parts;
+  p->status = reinterpret_cast<uint32_t *>(c);
+  p->ws_ml = reinterpret_cast<float *>(c + kStatusBytes);
+  p->ws_o = reinterpret_cast<float *>(c + kStatusBytes + (rows * 2 * sizeof(float) + 255) / 256 * 256);
+}
+
+int plan_attn(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits, AttnPlan *plan) {
+  (void)kv_dtype;
+  const int g = h / kvh;
+  plan->variant = 0;  // SIMT for every group size until the tensor-core variant lands
+  (void)g;
+  int part;
+  if (num_splits > 0) {
+    part = (max_seq_len + num_splits - 1) / num_splits;
+    part = std::max(32, (part + 31) / 32 * 32);
+  } else {
+    // Enough CTAs to keep 148 SMs x 3 resident CTAs busy for several waves and to
+    // even out ragged context lengths, without partitions so small that the
+    // pipeline fill and the partial write-back show up.
+    const long units = static_cast<long>(batch) * kvh;
+    const long target = 148L * 3 * 8;
+    long want_parts = (target + units - 1) / std::max(1L, units);
+    part = static_cast<int>((max_seq_len + want_parts - 1) / want_parts);
+    part = std::max(kMinPartTokens, std::min(1024, (part + 31) / 32 * 32));
+  }
+  plan->part_tokens = part;
+  plan->max_parts = std::max(1, (max_seq_len + part - 1) / part);
+  plan->ws_bytes = attn_workspace_bytes(batch, h, plan->max_parts);
+  return VT_OK;
+}
+
+int launch_attn_reduce(const AttnParams &p, int kv_dtype, cudaStream_t stream) {
+  dim3 grid(p.h, p.batch);
+  if (kv_dtype == VT_KV_FP8_E4M3)
+    attn_reduce_kernel<true><<<grid, kHeadDim, 0, stream>>>(p);
+  else
+    attn_reduce_kernel<false><<<grid, kHeadDim, 0, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;
+}
+
+}  // namespace vt
+
+extern "C" {
+
+int vt_append(const void *key, const void *value, int64_t key_stride, int64_t value_stride,
+              const uint64_t *k_table, const uint64_t *v_table, const int64_t *byte_off,
+              const int64_t *slot_ids, const int32_t *seq_lens, const int32_t *cache_seq_lens,
+              int max_seq_len, int batch, int kvh, int d, int kv_dtype, const float *k_scale,
+              const float *v_scale, void *stream) {
+  if (batch < 0 || kvh <= 0 || max_seq_len < 1) return VT_ERR_INVALID;
+  if (batch == 0) return VT_OK;
+  if (!key || !value || !k_table || !v_table || !byte_off || !slot_ids) return VT_ERR_INVALID;
+  if (d != vt::kHeadDim) return VT_ERR_UNSUPPORTED;
+  if (kv_dtype != VT_KV_BF16 && kv_dtype != VT_KV_FP8_E4M3) return VT_ERR_UNSUPPORTED;
+  if (kv_dtype == VT_KV_FP8_E4M3 && (!k_scale || !v_scale)) return VT_ERR_INVALID;
+  if (max_seq_len > 1 && (!seq_lens || !cache_seq_lens)) return VT_ERR_INVALID;
+  if (key_stride < static_cast<int64_t>(kvh) * d || value_stride < static_cast<int64_t>(kvh) * d) return VT_ERR_INVALID;
+  vt::AppendParams p{key, value, key_stride, value_stride, k_table, v_table, byte_off, slot_ids,
+                     seq_lens, cache_seq_lens, max_seq_len, batch, kvh, k_scale, v_scale};
+  return vt::launch_append(p, kv_dtype, static_cast<cudaStream_t>(stream));
+}
+
+int vt_kv_scales(const void *x, int64_t stride, int n_tokens, int kvh, int d, float *scale, void *stream) {
+  if (!x || !scale || n_tokens < 0 || kvh <= 0) return VT_ERR_INVALID;
+  if (d != vt::kHeadDim) return VT_ERR_UNSUPPORTED;
+  return vt::launch_kv_scales(x, stride, n_tokens, kvh, scale, static_cast<cudaStream_t>(stream));
+}
+
+int vt_decode_attn_workspace_bytes(int batch, int h, int d, int max_seq_len, size_t *bytes) {
+  if (!bytes || batch < 0 || h <= 0 || max_seq_len < 0) return VT_ERR_INVALID;
+  if (d != vt::kHeadDim) return VT_ERR_UNSUPPORTED;
+  *bytes = vt::attn_workspace_bound(std::max(batch, 1), h, std::max(max_seq_len, 1));
+  return VT_OK;
+}
+
+int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_stride,
+                   const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
+                   const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len,
+                   float scale, int kv_dtype, const float *k_scale, const float *v_scale,
+                   float *lse, void *workspace, size_t workspace_bytes, int num_splits,
+                   void *stream) {
+  if (batch < 0 || h <= 0 || kvh <= 0 || max_seq_len < 0 || num_splits < 0) return VT_ERR_INVALID;
+  if (batch == 0) return VT_OK;
+  if (!out || !q || !k_table || !v_table || !slot_ids || !seq_lens || !workspace) return VT_ERR_INVALID;
+  if (d != vt::kHeadDim || h % kvh != 0) return VT_ERR_UNSUPPORTED;
+  const int g = h / kvh;
+  if (g != 1 && g != 2 && g != 4 && g != 8 && g != 16) return VT_ERR_UNSUPPORTED;
+  if (kv_dtype != VT_KV_BF16 && kv_dtype != VT_KV_FP8_E4M3) return VT_ERR_UNSUPPORTED;
+  if (kv_dtype == VT_KV_FP8_E4M3 && (!k_scale || !v_scale)) return VT_ERR_INVALID;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride % 8) || (reinterpret_cast<uintptr_t>(workspace) & 255))
+    return VT_ERR_INVALID;
+  if (q_stride < static_cast<int64_t>(h) * d || out_stride < static_cast<int64_t>(h) * d) return VT_ERR_INVALID;
+  vt::AttnPlan plan;
+  vt::plan_attn(batch, h, kvh, std::max(max_seq_len, 1), kv_dtype, num_splits, &plan);
+  if (plan.ws_bytes > workspace_bytes) return VT_ERR_INVALID;
+  vt::AttnParams p{};
+  p.out = out; p.out_stride = out_stride; p.q = q; p.q_stride = q_stride;
+  p.k_table = k_table; p.v_table = v_table; p.slot_ids = slot_ids; p.seq_lens = seq_lens;
+  p.batch = batch; p.h = h; p.kvh = kvh; p.scale = scale; p.k_scale = k_scale; p.v_scale = v_scale;
+  p.lse = lse; p.part_tokens = plan.part_tokens; p.max_parts = plan.max_parts;
+  vt::carve_workspace(workspace, batch, h, plan.max_parts, &p);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int st = plan.variant == 0 ? vt::launch_attn_simt(p, kv_dtype, s) : vt::launch_attn_mma(p, kv_dtype, s);
+  if (st != VT_OK) return st;
+  if (plan.max_parts > 1) st = vt::launch_attn_reduce(p, kv_dtype, s);
+  return st;
+}
+
+int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits,
+                        int *part_tokens, int *max_parts, int *variant) {
+  if (batch < 0 || h <= 0 || kvh <= 0 || h % kvh != 0 || max_seq_len < 0 || num_splits < 0) return VT_ERR_INVALID;
+  vt::AttnPlan plan;
+  vt::plan_attn(std::max(batch, 1), h, kvh, std::max(max_seq_len, 1), kv_dtype, num_splits, &plan);
+  if (part_tokens) *part_tokens = plan.part_tokens;
+  if (max_parts) *max_parts = plan.max_parts;
+  if (variant) *variant = plan.variant;
+  return VT_OK;
+}
+
+int vt_decode_attn_status(void *workspace, void *stream, int *code) {
+  if (!workspace || !code) return VT_ERR_INVALID;
+  uint32_t word = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(&word, workspace, 4, cudaMemcpyDeviceToHost, s) != cudaSuccess) return VT_ERR_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return VT_ERR_CUDA;
+  *code = word == vt::kKernelErrMagic ? VT_ERR_KERNEL : VT_OK;
+  return VT_OK;
+}
+
+const char *vt_version(void) { return "vtensor-b200 0.1 sm_100a"; }
+
+const char *vt_strerror(int status) {
+  switch (status) {
+    case VT_OK: return "ok";
+    case VT_ERR_INVALID: return "invalid argument";
+    case VT_ERR_DRIVER: return "CUDA driver call failed";
+    case VT_ERR_POOL_EMPTY: return "chunk pool exhausted";
+    case VT_ERR_RESERVE: return "growth exceeds the reserved virtual range";
+    case VT_ERR_TIMEOUT: return "timed out waiting for a pending growth";
+    case VT_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case VT_ERR_CUDA: return "CUDA runtime call or kernel launch failed";
+    case VT_ERR_STATE: return "call not valid in the current state";
+    case VT_ERR_NO_DRIVER: return "libcuda.so.1 could not be loaded";
+    case VT_ERR_KERNEL: return "a kernel's bounded wait ran out";
+    default: return "unknown status";
+  }
+}
+
+}  // extern "C"

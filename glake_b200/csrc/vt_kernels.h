@@ -1,0 +1,53 @@
+// Host-visible launch interface of the CUDA kernels (internal to the library).
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace vt {
+
+struct AppendParams {
+  const void *key, *value;
+  int64_t key_stride, value_stride;  // elements
+  const uint64_t *k_table, *v_table;
+  const int64_t *byte_off, *slot_ids;
+  const int32_t *seq_lens, *cache_seq_lens;
+  int max_seq_len, batch, kvh;
+  const float *k_scale, *v_scale;
+};
+int launch_append(const AppendParams &p, int kv_dtype, cudaStream_t stream);
+int launch_kv_scales(const void *x, int64_t stride, int n_tokens, int kvh, float *scale, cudaStream_t stream);
+
+struct AttnParams {
+  void *out;  int64_t out_stride;     // bf16, elements per batch row
+  const void *q; int64_t q_stride;
+  const uint64_t *k_table, *v_table;
+  const int64_t *slot_ids;
+  const int32_t *seq_lens;
+  int batch, h, kvh;
+  float scale;                        // softmax scale (natural-log domain)
+  const float *k_scale, *v_scale;     // fp8 only
+  float *lse;                         // optional [batch, h]
+  int part_tokens;                    // tokens per split-K partition (multiple of 32)
+  int max_parts;                      // partitions per sequence the scratch is laid out for
+  uint32_t *status;                   // scratch status word
+  float *ws_ml;                       // [batch, h, max_parts, 2]  (max in log2 domain, sum)
+  float *ws_o;                        // [batch, h, max_parts, 128] unnormalised partial outputs
+};
+
+struct AttnPlan {
+  int part_tokens, max_parts;
+  int variant;       // 0 = SIMT (one kv head per CTA), 1 = tensor-core GQA
+  size_t ws_bytes;
+};
+// Picks the partition size and kernel variant for a problem; num_splits 0 = auto.
+int plan_attn(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits, AttnPlan *plan);
+size_t attn_workspace_bytes(int batch, int h, int max_parts);
+size_t attn_workspace_bound(int batch, int h, int max_seq_len);
+void carve_workspace(void *ws, int batch, int h, int max_parts, AttnParams *p);
+
+int launch_attn_simt(const AttnParams &p, int kv_dtype, cudaStream_t stream);
+int launch_attn_mma(const AttnParams &p, int kv_dtype, cudaStream_t stream);
+int launch_attn_reduce(const AttnParams &p, int kv_dtype, cudaStream_t stream);
+
+}  // namespace vt

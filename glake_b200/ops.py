@@ -1,0 +1,169 @@
+"""Custom-op layer with the reference's call signatures
+(GLakeServe/vllm/_custom_ops.py:34-52, :238-252 and the flash_attn_2_cuda.fwd_kvcache
+call at GLakeServe/vllm/attention/backends/xformers.py:407-430), forwarding to
+libvtensor's C ABI.  Tensors are only unwrapped to pointers and strides here; all
+work happens in the CUDA kernels.  Non-CUDA tensors are rejected: there is no
+CPU path.
+"""
+import ctypes
+from ctypes import byref, c_size_t, c_void_p
+
+import torch
+
+from ._lib import VT_KV_BF16, VT_KV_FP8_E4M3, check, lib
+
+_workspaces = {}
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("glake_b200 ops need CUDA tensors: there is no CPU fallback")
+
+
+def _kv_dtype(kv_cache_dtype):
+    if kv_cache_dtype in ("auto", "bf16", "bfloat16", None):
+        return VT_KV_BF16
+    if kv_cache_dtype in ("fp8", "fp8_e4m3"):
+        return VT_KV_FP8_E4M3
+    raise RuntimeError(f"unsupported kv_cache_dtype {kv_cache_dtype!r} (bf16 and fp8_e4m3 only)")
+
+
+def attn_workspace(device, batch, num_heads, head_size, max_seq_len):
+    """Scratch for the split-K partials, cached per device and grown on demand.
+    One buffer serves every layer because layers run back to back on one stream."""
+    need = c_size_t()
+    check(lib.vt_decode_attn_workspace_bytes(batch, num_heads, head_size, max_seq_len, byref(need)),
+          "vt_decode_attn_workspace_bytes")
+    key = (device.index if device.index is not None else torch.cuda.current_device())
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < need.value:
+        buf = torch.zeros(max(need.value, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def reshape_and_cache(key, value, key_cache, value_cache, slot_m, slot_mapping, seq_lens, cache_seq_lens,
+                      max_seq_len, num_kv_heads, head_size, kv_cache_dtype="auto", k_scale=None, v_scale=None):
+    """Append K/V rows into the slots' contiguous ranges.
+
+    Positional arguments as in the reference (csrc/cache.h:18-29): ``key_cache`` /
+    ``value_cache`` are int64 device tensors of base addresses indexed by slot id,
+    ``slot_m`` the per-entry destination byte offsets, ``slot_mapping`` the slot
+    ids, ``max_seq_len`` 1 for decode.  The keyword arguments add the fp8 e4m3
+    cache with per-kv-head scales (float32 device tensors of num_kv_heads)."""
+    _require_cuda(key, value, key_cache, value_cache, slot_m, slot_mapping)
+    if key.dtype != torch.bfloat16 or value.dtype != torch.bfloat16:
+        raise RuntimeError("reshape_and_cache: key/value must be bfloat16")
+    key = key.view(-1, num_kv_heads, head_size) if key.dim() == 2 else key
+    value = value.view(-1, num_kv_heads, head_size) if value.dim() == 2 else value
+    if key.stride(2) != 1 or key.stride(1) != head_size or value.stride(2) != 1 or value.stride(1) != head_size:
+        raise RuntimeError("reshape_and_cache: key/value rows must be contiguous [kv_heads, head_size]")
+    batch = slot_mapping.numel()
+    with torch.cuda.device(key.device):
+        check(lib.vt_append(_ptr(key), _ptr(value), key.stride(0), value.stride(0), _ptr(key_cache),
+                            _ptr(value_cache), _ptr(slot_m), _ptr(slot_mapping), _ptr(seq_lens),
+                            _ptr(cache_seq_lens), int(max_seq_len), batch, num_kv_heads, head_size,
+                            _kv_dtype(kv_cache_dtype), _ptr(k_scale), _ptr(v_scale), _stream()), "vt_append")
+
+
+def kv_scales(x, num_kv_heads, head_size):
+    """Per-kv-head scale = amax / 448 of x ([tokens, kv_heads, head_size] bf16)."""
+    _require_cuda(x)
+    x = x.view(-1, num_kv_heads, head_size)
+    out = torch.empty(num_kv_heads, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.vt_kv_scales(_ptr(x), x.stride(0), x.shape[0], num_kv_heads, head_size, _ptr(out), _stream()),
+              "vt_kv_scales")
+    return out
+
+
+def _decode(out, query, k_table, v_table, num_kv_heads, scale, seq_lens, max_seq_len, slot_ids, kv_dtype,
+            k_scale, v_scale, lse, num_splits):
+    batch, num_heads, head_size = query.shape
+    ws = attn_workspace(query.device, batch, num_heads, head_size, max_seq_len)
+    with torch.cuda.device(query.device):
+        check(lib.vt_decode_attn(_ptr(out), out.stride(0), _ptr(query), query.stride(0), c_void_p(int(k_table)),
+                                 c_void_p(int(v_table)), _ptr(slot_ids), _ptr(seq_lens), batch, num_heads,
+                                 num_kv_heads, head_size, int(max_seq_len), float(scale), kv_dtype, _ptr(k_scale),
+                                 _ptr(v_scale), _ptr(lse), _ptr(ws), ws.numel(), int(num_splits), _stream()),
+              "vt_decode_attn")
+
+
+def paged_attention_v1(out, query, key_cache, value_cache, num_kv_heads, scale, seq_lens, block_size, max_seq_len,
+                       alibi_slopes, kv_cache_dtype, kv_scale, slot_mapping, k_scale=None, v_scale=None,
+                       num_splits=0):
+    """Decode attention with the reference's vTensor signature (csrc/ops.h:6-19):
+    ``key_cache`` / ``value_cache`` are the device addresses (ints) of the per-layer
+    pointer tables, ``slot_mapping`` the slot ids.  ``block_size`` must be 1 (the
+    token-major contiguous layout, vllm/attention/ops/paged_attn.py:105)."""
+    _require_cuda(out, query, seq_lens, slot_mapping)
+    if alibi_slopes is not None:
+        raise RuntimeError("paged_attention_v1: ALiBi is not supported on the vTensor path")
+    if block_size != 1:
+        raise RuntimeError("paged_attention_v1: the vTensor layout is block_size 1")
+    if query.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise RuntimeError("paged_attention_v1: bf16 only")
+    kvd = _kv_dtype(kv_cache_dtype)
+    if kvd == VT_KV_FP8_E4M3 and k_scale is None:
+        k_scale = torch.full((num_kv_heads,), float(kv_scale), dtype=torch.float32, device=query.device)
+        v_scale = k_scale
+    _decode(out, query, key_cache, value_cache, num_kv_heads, scale, seq_lens, max_seq_len, slot_mapping, kvd,
+            k_scale, v_scale, None, num_splits)
+
+
+def fwd_kvcache(q, k_table_ptr, v_table_ptr, max_seq_len, num_kv_heads, batch, slot_mapping, k_new, v_new,
+                seq_lens, rotary_cos, rotary_sin, cache_batch_idx, block_table, alibi_slopes, out, softmax_scale,
+                causal, window_left, window_right, rotary_interleaved, num_splits, kv_cache_dtype="auto",
+                k_scale=None, v_scale=None):
+    """The 22-positional-argument call the reference's backend makes into its
+    flash-attention fork (xformers.py:407-430): q ``[B, 1, H, D]``, pointer-table
+    addresses, ``slot_mapping`` slot ids, ``seq_lens`` int32.  Returns ``(out, lse)``
+    with out ``[B, 1, H, D]`` and lse ``[B, H, 1]`` float32.  The arguments the
+    reference always passes as None / -1 must be None / -1 here."""
+    _require_cuda(q, slot_mapping, seq_lens)
+    for name, v in (("k_new", k_new), ("v_new", v_new), ("rotary_cos", rotary_cos), ("rotary_sin", rotary_sin),
+                    ("cache_batch_idx", cache_batch_idx), ("block_table", block_table),
+                    ("alibi_slopes", alibi_slopes)):
+        if v is not None:
+            raise RuntimeError(f"fwd_kvcache: {name} is not supported on the vTensor path")
+    if window_left != -1 or window_right != -1:
+        raise RuntimeError("fwd_kvcache: sliding window is not supported")
+    if q.dim() != 4 or q.shape[1] != 1:
+        raise RuntimeError("fwd_kvcache: decode call expects q of shape [B, 1, H, D]")
+    b, _, h, d = q.shape
+    q3 = q.view(b, h, d) if q.is_contiguous() else q[:, 0]
+    o = out if out is not None else torch.empty(b, 1, h, d, dtype=q.dtype, device=q.device)
+    lse = torch.empty(b, h, dtype=torch.float32, device=q.device)
+    _decode(o.view(b, h, d), q3, k_table_ptr, v_table_ptr, num_kv_heads, softmax_scale, seq_lens, max_seq_len,
+            slot_mapping, _kv_dtype(kv_cache_dtype), k_scale, v_scale, lse, 0)
+    return o, lse.unsqueeze(-1)
+
+
+def attn_plan(batch, num_heads, num_kv_heads, max_seq_len, kv_cache_dtype="auto", num_splits=0):
+    """(tokens per partition, partitions per sequence, kernel variant) the library
+    picks for this problem size."""
+    a, b, c = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+    check(lib.vt_decode_attn_plan(batch, num_heads, num_kv_heads, max_seq_len, _kv_dtype(kv_cache_dtype),
+                                  num_splits, byref(a), byref(b), byref(c)), "vt_decode_attn_plan")
+    return a.value, b.value, c.value
+
+
+def attn_status(device=None):
+    """VT_OK (0) unless an attention kernel's bounded wait ran out since the
+    workspace was created.  Synchronises the current stream."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    ws = _workspaces.get(dev.index if dev.index is not None else torch.cuda.current_device())
+    if ws is None:
+        return 0
+    code = ctypes.c_int()
+    check(lib.vt_decode_attn_status(_ptr(ws), _stream(), byref(code)), "vt_decode_attn_status")
+    return code.value

@@ -1,0 +1,239 @@
+/*
+ * libvtensor — C ABI of the B200 vTensor decode path.
+ *
+ * Three groups of entry points, each replacing one piece of GLakeServe:
+ *   1. the VMM allocator (vmm_allocator/vmm_allocator.{h,cpp}): a pool of 2 MiB
+ *      physical chunks and, per sequence slot, one contiguous virtual K range
+ *      and one V range per layer that grow by mapping chunks, never by copying;
+ *   2. the KV append (csrc/cache_kernels.cu reshape_and_cache);
+ *   3. single-query decode attention over those ranges
+ *      (csrc/attention/attention_kernels.cu paged_attention_v1 and the external
+ *      flash_attn_2_cuda.fwd_kvcache call in vllm/attention/backends/xformers.py).
+ *
+ * Conventions: every function returns an int status (VT_OK == 0), nothing
+ * throws across the boundary, handles are opaque, the caller owns q/k/v/out
+ * and passes the CUDA stream explicitly (a cudaStream_t cast to void*; NULL is
+ * the legacy default stream).  Kernel entry points only enqueue work; they
+ * never synchronise and never allocate.  All functions are thread-safe.
+ * File:line citations name the reference interface each entry point stands in
+ * for (paths inside the reference project, under GLakeServe/).
+ */
+#ifndef VTENSOR_H_
+#define VTENSOR_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status ------------------------------------------------------------ */
+enum {
+  VT_OK = 0,
+  VT_ERR_INVALID = 1,      /* bad argument (null, negative, misaligned, out of range) */
+  VT_ERR_DRIVER = 2,       /* a CUDA driver call failed; see vt_last_driver_error */
+  VT_ERR_POOL_EMPTY = 3,   /* not enough free physical chunks */
+  VT_ERR_RESERVE = 4,      /* growth would exceed the slot's reserved virtual range */
+  VT_ERR_TIMEOUT = 5,      /* bounded wait for a pending growth ran out */
+  VT_ERR_UNSUPPORTED = 6,  /* shape / dtype outside what the kernels implement */
+  VT_ERR_CUDA = 7,         /* kernel launch or runtime call failed */
+  VT_ERR_STATE = 8,        /* call not valid in the object's current state */
+  VT_ERR_NO_DRIVER = 9,    /* libcuda could not be loaded (no GPU on this machine) */
+  VT_ERR_KERNEL = 10       /* a kernel reported a bounded wait that ran out */
+};
+
+/* Human-readable text for a status code (static storage). */
+const char *vt_strerror(int status);
+/* CUresult of the last failing driver call on the calling thread, 0 if none.
+ * Replaces the reference's print-and-assert(0) (vmm_allocator.h:19-42). */
+int vt_last_driver_error(void);
+/* Library version string, e.g. "vtensor-b200 0.1 sm_100a". */
+const char *vt_version(void);
+
+/* ---- KV element types -------------------------------------------------- */
+enum {
+  VT_KV_BF16 = 0,     /* 2-byte cache elements, bit-exact copy of the inputs      */
+  VT_KV_FP8_E4M3 = 1  /* 1-byte e4m3 (max 448), stored = sat(x / scale[kv_head]) */
+};
+
+/* ---- allocator --------------------------------------------------------- */
+typedef struct vt_pool vt_pool;
+typedef struct vt_seg vt_seg;
+typedef struct vt_table vt_table;
+
+typedef struct vt_stats {
+  uint64_t chunks_total, chunks_free;
+  uint64_t chunk_bytes;
+  uint64_t map_calls, unmap_calls, set_access_calls; /* driver calls issued   */
+  uint64_t map_ns;                                   /* wall time spent in them */
+  uint64_t async_requests, async_completed, async_failed;
+  uint64_t segments;
+} vt_stats;
+
+/* Routes every driver call of pools created AFTERWARDS to an in-process fake
+ * (no GPU needed; addresses are synthetic).  For host-side tests only. */
+int vt_use_mock_driver(int enable);
+/* Mock only: make the n-th next call (1-based; 0 disables) of the named driver
+ * entry point ("cuMemCreate", "cuMemAddressReserve", "cuMemMap",
+ * "cuMemSetAccess", "cuMemUnmap", "cuMemAlloc", "cuMemcpyHtoD") fail once. */
+int vt_mock_fail_nth(const char *call, int nth);
+/* Mock only: delay every cuMemMap by this many microseconds (tests the bounded wait). */
+int vt_mock_map_delay_us(int us);
+
+/* Creates n_chunks physical chunks of chunk_bytes (0 = 2 MiB; must be a multiple
+ * of the device's allocation granularity) on `device` and starts the background
+ * growth worker.  Replaces init_physical_handle (vmm_allocator.cpp:113-151) and
+ * PhyBlock (vmm_allocator.cpp:154-174). */
+int vt_pool_create(int device, size_t n_chunks, size_t chunk_bytes, vt_pool **out);
+/* Stops the worker, releases every chunk.  All segments and tables of the pool
+ * must have been destroyed first (VT_ERR_STATE otherwise). */
+int vt_pool_destroy(vt_pool *pool);
+/* Free chunk count; replaces showFreeBlocks (vmm_allocator.cpp:472-474). */
+int vt_pool_free_chunks(vt_pool *pool, size_t *out);
+int vt_pool_stats(vt_pool *pool, vt_stats *out);
+
+/* One sequence slot: reserves 2 * n_layers virtual ranges of reserve_bytes each
+ * (rounded up to the chunk size) in ONE address reservation, K of layer l at
+ * base + (2l) * reserve, V at base + (2l + 1) * reserve, and maps premap_bytes
+ * of every range right away.  Replaces the KVcacheSegment constructor
+ * (vmm_allocator.cpp:177-211). */
+int vt_seg_create(vt_pool *pool, int n_layers, size_t reserve_bytes, size_t premap_bytes, vt_seg **out);
+/* Unmaps everything, returns the chunks, frees the address reservation. */
+int vt_seg_destroy(vt_seg *seg);
+/* Base device address of layer's K / V range; replaces getKeyDevicePtr /
+ * getValueDevicePtr (vmm_allocator.cpp:299-305). */
+int vt_seg_k_ptr(vt_seg *seg, int layer, uint64_t *dptr);
+int vt_seg_v_ptr(vt_seg *seg, int layer, uint64_t *dptr);
+/* Logical fill in bytes per range; replaces get_used_slot / set_used_size
+ * (vmm_allocator.cpp:339-346). */
+int vt_seg_used(vt_seg *seg, size_t *bytes);
+int vt_seg_set_used(vt_seg *seg, size_t bytes);
+/* Mapped bytes per range (the reference's actual_size) and the reservation. */
+int vt_seg_mapped(vt_seg *seg, size_t *bytes);
+int vt_seg_reserved(vt_seg *seg, size_t *bytes);
+/* Synchronously map chunks until every range has >= bytes_needed mapped.
+ * Replaces expandMultiSegment / the prefill-side copy_kv_cache
+ * (vmm_allocator.cpp:214-297, :322-337) without the fixed 100-token headroom. */
+int vt_seg_grow(vt_seg *seg, size_t bytes_needed);
+/* Queue a growth of n_chunks per range on the pool's worker thread and return
+ * at once.  Replaces eagerExtend + the eagerly_extend thread
+ * (vmm_allocator.cpp:307-320, :40-72). */
+int vt_seg_grow_async(vt_seg *seg, int n_chunks);
+/* 1 if no growth is pending for the segment; replaces query_shm
+ * (vmm_allocator.cpp:85-92). */
+int vt_seg_ready(vt_seg *seg, int *ready);
+/* Blocks until no growth is pending or timeout_us elapsed (VT_ERR_TIMEOUT).
+ * Returns the status of the last finished background growth.  Replaces the
+ * unbounded spin in vllm/model_executor/models/llama.py:322-326. */
+int vt_seg_wait(vt_seg *seg, uint64_t timeout_us);
+/* Unmap everything beyond keep_bytes (rounded up to a chunk) in every range,
+ * return those chunks, reset used to 0.  Replaces release_seq
+ * (vmm_allocator.cpp:383-421); keep_bytes = 0 is preempt_seq (:348-381). */
+int vt_seg_release(vt_seg *seg, size_t keep_bytes);
+
+/* The decode-step bookkeeping of extend_kv_cache_batch (vmm_allocator.h:138-168)
+ * for n segments in one call: for entry i, if set_used_tokens[i] > 0 then
+ * used = set_used_tokens[i] * kv_size; out_offsets[i] = used; then
+ *   gen != 0 (decode):  used += token_bytes[i]; if the rows would not fit into
+ *                       mapped memory the call first waits up to wait_us for the
+ *                       slot's pending background growth (VT_ERR_TIMEOUT) and, if
+ *                       that does not cover them, maps synchronously;
+ *   gen == 0 (prefill): grow synchronously to used + token_bytes[i], used += token_bytes[i].
+ * Nothing is committed when any entry fails.
+ * set_used_tokens may be NULL. */
+int vt_extend_batch(vt_seg *const *segs, int n, const int64_t *set_used_tokens,
+                    const uint64_t *token_bytes, uint64_t kv_size, int gen,
+                    uint64_t wait_us, int64_t *out_offsets);
+
+/* Device array of n_slots 8-byte base addresses indexed by slot id; replaces
+ * KVCache (vmm_allocator.cpp:458-470). */
+int vt_table_create(vt_pool *pool, int n_slots, vt_table **out);
+int vt_table_destroy(vt_table *tbl);
+int vt_table_set(vt_table *tbl, int slot, uint64_t dptr);
+/* Fills slots [0, n) of k_tbl / v_tbl with the layer's K / V base of segs[i];
+ * replaces the per-layer loop of copy_kv_cache (vmm_allocator.h:170-182). */
+int vt_table_fill(vt_table *k_tbl, vt_table *v_tbl, vt_seg *const *segs, int n, int layer);
+int vt_table_dptr(vt_table *tbl, uint64_t *dptr);
+
+/* Debug helpers: synchronous copies between host memory and an address inside a
+ * mapped range (or a table).  Replace write_string / read_string
+ * (vmm_allocator.cpp:423-446).  They synchronise the device. */
+int vt_pool_read(vt_pool *pool, void *dst_host, uint64_t src_dptr, size_t bytes);
+int vt_pool_write(vt_pool *pool, uint64_t dst_dptr, const void *src_host, size_t bytes);
+
+/* ---- KV append --------------------------------------------------------- */
+/* Writes new K/V rows into the slots' ranges.  Replaces reshape_and_cache
+ * (csrc/cache_kernels.cu:153-200, :257-297; declared csrc/cache.h:18-29).
+ *   key/value     bf16 [tokens, kvh, d], dim-0 stride in ELEMENTS (fused-qkv views allowed)
+ *   k_table/v_table  device arrays of base addresses indexed by slot id
+ *   byte_off[i]   device int64: destination byte offset of entry i's first row
+ *                 (what extend_kv_cache_batch returned); negative = skip entry
+ *   slot_ids[i]   device int64: slot of entry i
+ *   max_seq_len   1 = decode (one row per entry, source row i); otherwise
+ *                 prefill: entry i writes seq_lens[i] rows read from source rows
+ *                 cache_seq_lens[i] + t (both device int32, required then)
+ *   kv_dtype      VT_KV_BF16: bit-exact copy, row = kvh*d*2 bytes;
+ *                 VT_KV_FP8_E4M3: byte = sat_e4m3(x / scale[kv_head]),
+ *                 row = kvh*d bytes, k_scale/v_scale device float[kvh]
+ *                 (fp8 storage has no counterpart on the reference's vTensor
+ *                 path; arithmetic follows csrc/quantization/fp8/nvidia/quant_utils.cuh:467-479)
+ * d must be 128. */
+int vt_append(const void *key, const void *value, int64_t key_stride, int64_t value_stride,
+              const uint64_t *k_table, const uint64_t *v_table, const int64_t *byte_off,
+              const int64_t *slot_ids, const int32_t *seq_lens, const int32_t *cache_seq_lens,
+              int max_seq_len, int batch, int kvh, int d, int kv_dtype, const float *k_scale,
+              const float *v_scale, void *stream);
+
+/* Per-kv-head scale = amax / 448 over n_tokens rows of x (bf16 [n_tokens, kvh, d],
+ * dim-0 stride in elements), 1.0 for an all-zero head.  scale: device float[kvh].
+ * No counterpart in the reference (its scales come from a checkpoint file,
+ * vllm/model_executor/model_loader/weight_utils.py:296-333). */
+int vt_kv_scales(const void *x, int64_t stride, int n_tokens, int kvh, int d, float *scale,
+                 void *stream);
+
+/* ---- decode attention -------------------------------------------------- */
+/* Scratch bytes vt_decode_attn needs for this problem size (max_seq_len is an
+ * upper bound of every seq_lens entry).  The scratch holds the split-K partial
+ * results; the caller allocates it once and may reuse it for every layer. */
+int vt_decode_attn_workspace_bytes(int batch, int h, int d, int max_seq_len, size_t *bytes);
+
+/* out[i, hq, :] = softmax_t(scale * q[i, hq] . K[t, hq / (h / kvh)]) . V[t, hq / (h / kvh)]
+ * over tokens t < seq_lens[i] of slot slot_ids[i]; element (t, kv_head, x) of a
+ * range sits at ((t * kvh + kv_head) * d + x) elements from its base.
+ * Replaces paged_attention_v1 as modified for vTensor
+ * (csrc/attention/attention_kernels.cu:93-420, :721-737; csrc/ops.h:6-19) and
+ * the decode call of fwd_kvcache (vllm/attention/backends/xformers.py:407-430).
+ *   out, q        bf16 [batch, h, d]; strides of dim 0 in elements
+ *   seq_lens      device int32 [batch] (context INCLUDING the appended token)
+ *   max_seq_len   host upper bound of seq_lens, sizes the split-K grid
+ *   scale         softmax scale (1/sqrt(d) in the reference)
+ *   kv_dtype, k_scale, v_scale   as for vt_append
+ *   lse           optional device float [batch, h]: log-sum-exp of the scaled
+ *                 logits (second return value of fwd_kvcache); may be NULL
+ *   workspace     >= vt_decode_attn_workspace_bytes(...) bytes, 256-byte aligned
+ *   num_splits    0 = choose; otherwise the number of token partitions per sequence
+ * Long contexts are split over tokens; a second kernel merges the partial
+ * results.  d must be 128; h / kvh in {1,2,4,8,16}; no ALiBi, no sliding window. */
+int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_stride,
+                   const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
+                   const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len,
+                   float scale, int kv_dtype, const float *k_scale, const float *v_scale,
+                   float *lse, void *workspace, size_t workspace_bytes, int num_splits,
+                   void *stream);
+
+/* What vt_decode_attn will do for this problem: tokens per split-K partition,
+ * partitions per sequence the scratch is laid out for (> 1 means the merge
+ * kernel runs too), and the kernel variant (0 = SIMT, 1 = tensor-core GQA).
+ * Introspection for benchmarks and tests; no counterpart in the reference. */
+int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits,
+                        int *part_tokens, int *max_parts, int *variant);
+
+/* Reads (synchronously, on `stream`) the error word the attention kernels set
+ * when one of their bounded waits ran out: *code = 0 or VT_ERR_KERNEL. */
+int vt_decode_attn_status(void *workspace, void *stream, int *code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* VTENSOR_H_ */
