@@ -1,0 +1,336 @@
+// Single-query decode attention, persistent "flat" schedule on the tensor-core
+// tile engine of vt_attn_mma.cu (same shared-memory geometry, same per-warp math).
+//
+// Why: with one CTA per (sequence, token partition) every CTA pays a pipeline
+// fill, ragged context lengths leave a tail wave, and a second kernel merges the
+// partitions.  Here the whole batch is one list of tiles (16 groups of 1 KiB of
+// K and of V): stream (sequence b, kv-head slab) contributes
+// ceil(L_b / tile_tokens) tiles, streams are laid end to end, and CTA c of N
+// takes tiles [c*T/N, (c+1)*T/N).  N = 2 x SM count CTAs are all resident, each
+// moves the same number of bytes, and its copy ring never drains: the producer
+// warp simply keeps issuing bulk copies across stream boundaries.
+//
+// A maximal run of a CTA's tiles inside one stream is a "piece".  A piece that
+// covers its whole stream is final.  Otherwise the CTA writes the piece's
+// unnormalised state (O[128], running max, running sum per q head and consumer
+// warp) to scratch and takes a ticket on the stream's counter; whoever draws the
+// last ticket merges all pieces of the stream and writes the output.  Nobody
+// waits for anybody, so the kernel cannot hang on a missing peer.  A CTA has at
+// most two non-final pieces (its first and its last), hence two scratch slots
+// per CTA regardless of context length.
+//
+// Roofline: HBM.  Algorithmic bytes per (sequence, kv head): L * 2 * 128 * 2.
+#include "../../include/vtensor.h"
+#include "vt_device.cuh"
+#include "vt_kernels.h"
+#include "vt_mma.cuh"
+
+namespace vt {
+namespace {
+
+constexpr int kStages = kMmaStages;
+constexpr int kCWarps = kMmaCWarps;
+constexpr int kThreads = kMmaThreads;
+constexpr int kRing = kStages * kStageB;
+constexpr int kPartRow = kFlatPartRow;   // floats per published (q head, warp) state: O[128], max, sum, pad
+
+__host__ __device__ constexpr int flat_smem_bytes(int batch) {
+  return kRing + 2 * kStages * 8 + 16 + (batch + 1) * 4;
+}
+
+struct Piece {
+  int b, slab, tile_begin, tile_end, tiles_in_stream;
+  long long stream_begin;  // global index of the stream's first tile
+};
+
+// Locates the stream holding global tile `tau` and the run of tiles this CTA
+// owns inside it.  prefix[b] = global index of sequence b's first tile.
+__device__ __forceinline__ Piece locate(const int *prefix, int batch, int slabs, long long tau, long long tau_end) {
+  int lo = 0, hi = batch;  // largest b with prefix[b] <= tau
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (prefix[mid] <= tau) lo = mid; else hi = mid;
+  }
+  Piece pc;
+  pc.b = lo;
+  const int per_slab = (prefix[lo + 1] - prefix[lo]) / slabs;
+  const int rem = static_cast<int>(tau - prefix[lo]);
+  pc.slab = rem / per_slab;
+  pc.tile_begin = rem % per_slab;
+  pc.tiles_in_stream = per_slab;
+  pc.stream_begin = prefix[lo] + static_cast<long long>(pc.slab) * per_slab;
+  const long long room = tau_end - tau;
+  pc.tile_end = static_cast<int>(min(static_cast<long long>(per_slab), pc.tile_begin + room));
+  return pc;
+}
+
+// CTA that owns global tile tau when CTA c starts at floor(c * T / N).
+__device__ __forceinline__ int owner_of(long long tau, long long total, int n_ctas) {
+  return static_cast<int>(((tau + 1) * n_ctas - 1) / total);
+}
+
+template <int NB, int HS, int R>
+__global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
+  static_assert(HS * R == kCWarps, "one consumer warp per (kv head, row of a group)");
+  extern __shared__ __align__(128) unsigned char smem[];
+  constexpr int TILE_TOK = kGroupsPerTile * R;
+  constexpr int HEADS = NB * 8;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kRing);
+  int *flags = reinterpret_cast<int *>(smem + kRing + 2 * kStages * 8);   // [0] = "this CTA merges"
+  int *prefix = flags + 4;                                                // [batch + 1]
+  const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
+  const uint32_t ring0 = smem_u32(smem);
+
+  const int g = p.h / p.kvh;
+  const int slabs = p.kvh / HS;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, kCWarps);
+    }
+    mbar_fence_init();
+  }
+  // tiles per sequence, then an exclusive prefix (batch is small: one warp scans it)
+  for (int i = threadIdx.x; i < p.batch; i += kThreads)
+    prefix[i + 1] = ((max(p.seq_lens[i], 0) + TILE_TOK - 1) / TILE_TOK) * slabs;
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int base = 0; base < p.batch; base += 32) {
+      const int i = base + lane;
+      int v = i < p.batch ? prefix[i + 1] : 0;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, off);
+        if (lane >= off) v += n;
+      }
+      if (i < p.batch) prefix[i + 1] = carry + v;
+      carry += __shfl_sync(0xffffffffu, v, 31);
+    }
+    if (lane == 0) prefix[0] = 0;
+  }
+  __syncthreads();
+  const long long total = prefix[p.batch];
+  // Only min(grid, total) CTAs take part, so that every participating CTA owns at
+  // least one tile and the piece count of a stream is a plain difference.
+  const int n_ctas = static_cast<int>(min(static_cast<long long>(gridDim.x), total));
+  const bool active = static_cast<int>(blockIdx.x) < n_ctas;
+  const long long tau0 = active ? total * blockIdx.x / n_ctas : 0;
+  const long long tau1 = active ? total * (blockIdx.x + 1) / n_ctas : 0;
+
+  if (warp == kCWarps) {
+    // ---------------- producer warp ----------------
+    // lanes 0..15 fetch the K groups of a tile, lanes 16..31 the V groups
+    const int grp = lane & 15;
+    const uint32_t dst_lane = (lane < 16 ? 0 : kTileB) + grp * kPitch;
+    const size_t tok_pitch = static_cast<size_t>(p.kvh) * kRowB;
+    const uint64_t policy = l2_policy_evict_first();
+    int it = 0;  // tiles issued by this CTA: ring position and barrier phase
+    for (long long tau = tau0; tau < tau1;) {
+      const Piece pc = locate(prefix, p.batch, slabs, tau, tau1);
+      const int64_t slot = p.slot_ids[pc.b];
+      const int seq_len = p.seq_lens[pc.b];
+      const char *base = reinterpret_cast<const char *>(lane < 16 ? p.k_table[slot] : p.v_table[slot]) +
+                         static_cast<size_t>(pc.slab) * HS * kRowB;
+      for (int tile = pc.tile_begin; tile < pc.tile_end; ++tile, ++it) {
+        const int s = it % kStages;
+        if (it >= kStages && !mbar_wait(empty0 + 8 * s, ((it / kStages) - 1) & 1)) {
+          if (lane == 0) atomicExch(p.status, kKernelErrMagic);
+          return;
+        }
+        const int t0 = tile * TILE_TOK;
+        const int nt = min(TILE_TOK, seq_len - t0);
+        if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2u * nt * HS * kRowB);
+        __syncwarp();
+        const int rows = min(R, nt - grp * R);   // valid token rows of this lane's group
+        if (rows > 0)
+          bulk_g2s_hint(ring0 + s * kStageB + dst_lane, base + static_cast<size_t>(t0 + grp * R) * tok_pitch,
+                        rows * HS * kRowB, full0 + 8 * s, policy);
+      }
+      tau += pc.tile_end - pc.tile_begin;
+    }
+    return;
+  }
+
+  // ---------------- consumer warps ----------------
+  const int hs = warp % HS, rr = warp / HS;      // kv head within the slab, row within each group
+  const uint32_t row_off = (rr * HS + hs) * kRowB;
+  const uint32_t k_off = k_lane_offset(lane, row_off), v_off = v_lane_offset(lane, row_off);
+  const float sl2 = p.scale * 1.4426950408889634f;
+  const int tid = threadIdx.x;  // 0..127
+  __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
+
+  // Sequences without context produce zeros; nobody owns a tile of theirs.
+  if (blockIdx.x == 0) {
+    for (int b = 0; b < p.batch; ++b)
+      if (prefix[b + 1] == prefix[b]) {
+        for (int i = tid; i < p.h * kHeadDim; i += kCWarps * 32) out[b * p.out_stride + i] = __float2bfloat16(0.f);
+        if (p.lse && tid < p.h) p.lse[b * p.h + tid] = -INFINITY;
+      }
+  }
+
+  // A wait that runs out marks the warp as failed; it then skips the remaining
+  // tiles but still walks through every piece and every barrier below, so the
+  // other consumer warps are never left waiting for it.
+  bool failed = false;
+  int it = 0;
+  bool first_piece = true;
+  for (long long tau = tau0; tau < tau1;) {
+    const Piece pc = locate(prefix, p.batch, slabs, tau, tau1);
+    const int seq_len = p.seq_lens[pc.b];
+    const int kv_head = pc.slab * HS + hs;
+    WarpAttn<NB> st;
+    st.start(static_cast<const __nv_bfloat16 *>(p.q) + pc.b * p.q_stride + kv_head * g * kHeadDim, g, lane);
+    for (int tile = pc.tile_begin; tile < pc.tile_end; ++tile, ++it) {
+      const int s = it % kStages;
+      if (!failed && !mbar_wait(full0 + 8 * s, (it / kStages) & 1)) failed = true;
+      if (failed) continue;
+      const int tok0 = tile * TILE_TOK + rr;      // token of fragment row 0
+      if (tok0 < seq_len)
+        st.tile(ring0 + s * kStageB, smem + s * kStageB, k_off, v_off, row_off,
+                min(16, (seq_len - tok0 + R - 1) / R), sl2, lane);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + 8 * s);
+    }
+    st.finish_sums();
+
+    const bool whole = pc.tile_begin == 0 && pc.tile_end == pc.tiles_in_stream;
+    if (R == 1 && whole) {
+      // This warp saw every token of its kv head: write the result from registers.
+      const int r4 = lane >> 2, c4 = lane & 3;
+#pragma unroll
+      for (int nb = 0; nb < NB; ++nb) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int head = nb * 8 + 2 * c4 + e;
+          if (head < g) {
+            const float inv = 1.0f / st.lrun[nb][e];   // > 0: a stream holds at least one token
+            const int hq = kv_head * g + head;
+            __nv_bfloat16 *dst = out + pc.b * p.out_stride + hq * kHeadDim;
+#pragma unroll
+            for (int mb = 0; mb < 8; ++mb) {
+              dst[mb * 16 + r4] = __float2bfloat16(st.o[nb][mb][e] * inv);
+              dst[mb * 16 + r4 + 8] = __float2bfloat16(st.o[nb][mb][2 + e] * inv);
+            }
+            if (p.lse && r4 == 0)
+              p.lse[pc.b * p.h + hq] = (st.mrun[nb][e] + log2f(st.lrun[nb][e])) * 0.6931471805599453f;
+          }
+        }
+      }
+    } else {
+      // Publish this piece, draw a ticket, and merge the stream if it was the last one.
+      const int slot_id = first_piece ? 0 : 1;
+      st.template store<kPartRow>(
+          p.fl_part + ((static_cast<size_t>(blockIdx.x) * 2 + slot_id) * kCWarps + warp) * HEADS * kPartRow, lane);
+      __threadfence();
+      named_bar_sync(1, kCWarps * 32);
+      const long long s_begin = pc.stream_begin, s_end = pc.stream_begin + pc.tiles_in_stream;
+      const int c_first = owner_of(s_begin, total, n_ctas), c_last = owner_of(s_end - 1, total, n_ctas);
+      const int n_pieces = c_last - c_first + 1;
+      if (tid == 0) {
+        unsigned *ctr = p.fl_count + pc.b * slabs + pc.slab;
+        const unsigned old = atomicAdd(ctr, 1u);
+        const int last = old + 1 == static_cast<unsigned>(n_pieces);
+        if (last) *ctr = 0u;   // leaves the counters clean for the next launch
+        flags[0] = last;
+      }
+      named_bar_sync(1, kCWarps * 32);
+      const bool merger = flags[0] != 0;
+      named_bar_sync(1, kCWarps * 32);   // flags[0] may be rewritten by the next piece
+      if (merger) {
+        __threadfence();
+        // Sources of one q head: (piece c, consumer warp r * HS + hh).  Heads are
+        // dealt round-robin to the four warps; inside a warp lane i first fetches
+        // (max, sum) of source i, the warp agrees on the stream maximum, then every
+        // lane accumulates its 4 output dims over the sources with independent
+        // 16-byte loads.  Streams cut into more than 32 sources go in rounds.
+        const int n_src = n_pieces * R;
+        for (int item = warp; item < HS * g; item += kCWarps) {
+          const int hh = item / g, head = item % g;
+          float M = -INFINITY, L = 0.f;
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int s0 = 0; s0 < n_src; s0 += 32) {
+            const int i = s0 + lane;
+            const float *mine = nullptr;
+            float mi = -INFINITY, li = 0.f;
+            if (i < n_src) {
+              const int c = c_first + i / R, r = i % R;
+              // the stream is CTA c's first piece iff it already runs at c's first tile
+              const int sl = (s_begin <= total * c / n_ctas) ? 0 : 1;
+              mine = p.fl_part + (((static_cast<size_t>(c) * 2 + sl) * kCWarps + r * HS + hh) * HEADS + head) * kPartRow;
+              mi = __ldcg(mine + 128);
+              li = __ldcg(mine + 129);
+            }
+            float mx = mi;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+            const float Mn = fmaxf(M, mx);
+            const float rescale = exp2f(M - Mn);   // 0 on the first round (M = -inf)
+            const float fi = i < n_src ? exp2f(mi - Mn) : 0.f;
+            float ls = fi * li;
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, off);
+            L = L * rescale + ls;
+            acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
+            M = Mn;
+            const int cnt = min(32, n_src - s0);
+            for (int j = 0; j < cnt; ++j) {
+              const float f = __shfl_sync(0xffffffffu, fi, j);
+              const float *src = reinterpret_cast<const float *>(
+                  __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(mine), j));
+              const float4 v = __ldcg(reinterpret_cast<const float4 *>(src) + lane);
+              acc.x = fmaf(f, v.x, acc.x); acc.y = fmaf(f, v.y, acc.y);
+              acc.z = fmaf(f, v.z, acc.z); acc.w = fmaf(f, v.w, acc.w);
+            }
+          }
+          const int hq = (pc.slab * HS + hh) * g + head;
+          const float inv = 1.0f / L;
+          uint2 packed;
+          packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+          packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+          *reinterpret_cast<uint2 *>(out + pc.b * p.out_stride + hq * kHeadDim + lane * 4) = packed;
+          if (p.lse && lane == 0) p.lse[pc.b * p.h + hq] = (M + log2f(L)) * 0.6931471805599453f;
+        }
+      }
+    }
+    first_piece = false;
+    tau += pc.tile_end - pc.tile_begin;
+  }
+  if (failed && lane == 0) atomicExch(p.status, kKernelErrMagic);
+}
+
+template <int NB, int HS, int R>
+int launch(const AttnParams &p, cudaStream_t stream) {
+  const int smem = flat_smem_bytes(p.batch);
+  static int configured = 0;
+  if (configured < smem) {
+    if (cudaFuncSetAttribute(attn_flat_kernel<NB, HS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
+      return VT_ERR_CUDA;
+    configured = smem;
+  }
+  attn_flat_kernel<NB, HS, R><<<p.n_ctas, kThreads, smem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;
+}
+
+template <int NB>
+int launch_nb(const AttnParams &p, cudaStream_t stream) {
+  if (p.kvh % 4 == 0) return launch<NB, 4, 1>(p, stream);
+  if (p.kvh == 2) return launch<NB, 2, 2>(p, stream);
+  if (p.kvh == 1) return launch<NB, 1, 4>(p, stream);
+  return VT_ERR_UNSUPPORTED;
+}
+
+}  // namespace
+
+bool attn_flat_supports(int batch, int h, int kvh, int kv_dtype) {
+  return attn_mma_supports(h, kvh, kv_dtype) && batch <= kFlatMaxBatch;
+}
+
+int launch_attn_flat(const AttnParams &p, int kv_dtype, cudaStream_t stream) {
+  if (!attn_flat_supports(p.batch, p.h, p.kvh, kv_dtype)) return VT_ERR_UNSUPPORTED;
+  return (p.h / p.kvh) <= 8 ? launch_nb<1>(p, stream) : launch_nb<2>(p, stream);
+}
+
+}  // namespace vt

@@ -1,6 +1,8 @@
 // Split-K planning, the partial-result merge kernel, and the C entry points of
 // the device-side path.
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "../../include/vtensor.h"
 #include "vt_device.cuh"
@@ -43,9 +45,20 @@ size_t attn_workspace_bytes(int batch, int h, int max_parts) {
   return kStatusBytes + ml + rows * kHeadDim * sizeof(float);
 }
 
+static size_t flat_counter_bytes(int batch, int kvh) {
+  return (static_cast<size_t>(batch) * kvh * sizeof(unsigned) + 255) / 256 * 256;
+}
+static size_t flat_workspace_bytes(int batch, int h, int kvh, bool worst_case = false) {
+  const int heads = (!worst_case && (h / kvh) <= 8) ? 8 : 16;
+  return kStatusBytes + flat_counter_bytes(batch, kvh) +
+         static_cast<size_t>(kFlatMaxCtas) * 2 * 4 * heads * kFlatPartRow * sizeof(float);
+}
+
 size_t attn_workspace_bound(int batch, int h, int max_seq_len) {
   const int parts = std::max(1, (max_seq_len + kMinPartTokens - 1) / kMinPartTokens);
-  return attn_workspace_bytes(batch, h, parts);
+  // the flat schedule's scratch does not depend on the context length; h stands in
+  // for the kv-head count (its upper bound) when sizing the ticket counters
+  return std::max(attn_workspace_bytes(batch, h, parts), flat_workspace_bytes(batch, h, h, true));
 }
 
 void carve_workspace(void *ws, int batch, int h, int max_parts, AttnParams *p) {
@@ -56,11 +69,40 @@ void carve_workspace(void *ws, int batch, int h, int max_parts, AttnParams *p) {
   p->ws_o = reinterpret_cast<float *>(c + kStatusBytes + (rows * 2 * sizeof(float) + 255) / 256 * 256);
 }
 
+static void carve_flat(void *ws, int batch, int kvh, AttnParams *p) {
+  char *c = static_cast<char *>(ws);
+  p->status = reinterpret_cast<uint32_t *>(c);
+  p->fl_count = reinterpret_cast<unsigned *>(c + kStatusBytes);
+  p->fl_part = reinterpret_cast<float *>(c + kStatusBytes + flat_counter_bytes(batch, kvh));
+}
+
+// Two resident CTAs per SM of the current device.
+static int flat_grid() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 2 * 148;
+  if (cached[dev] == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    cached[dev] = std::min(2 * sms, kFlatMaxCtas);
+  }
+  return cached[dev];
+}
+
 int plan_attn(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits, AttnPlan *plan) {
-  (void)kv_dtype;
   const int g = h / kvh;
-  plan->variant = 0;  // SIMT for every group size until the tensor-core variant lands
+  // Tensor-core engine wherever it applies (bf16 KV) — on the flat persistent
+  // schedule unless the caller asks for explicit splits — SIMT otherwise (fp8 KV).
   (void)g;
+  plan->variant = attn_mma_supports(h, kvh, kv_dtype) ? 1 : 0;
+  if (num_splits == 0 && attn_flat_supports(batch, h, kvh, kv_dtype)) plan->variant = 2;
+  // Tuning overrides (read per call; meant for benchmarking, not for production):
+  //   VT_ATTN_VARIANT=simt|mma   VT_ATTN_PART_TOKENS=<multiple of 32>
+  if (const char *v = getenv("VT_ATTN_VARIANT")) {
+    if (!strcmp(v, "simt")) plan->variant = 0;
+    if (!strcmp(v, "mma") && attn_mma_supports(h, kvh, kv_dtype)) plan->variant = 1;
+    if (!strcmp(v, "flat") && attn_flat_supports(batch, h, kvh, kv_dtype)) plan->variant = 2;
+  }
   int part;
   if (num_splits > 0) {
     part = (max_seq_len + num_splits - 1) / num_splits;
@@ -75,9 +117,17 @@ int plan_attn(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_
     part = static_cast<int>((max_seq_len + want_parts - 1) / want_parts);
     part = std::max(kMinPartTokens, std::min(1024, (part + 31) / 32 * 32));
   }
+  if (const char *v = getenv("VT_ATTN_PART_TOKENS")) {
+    const int forced = atoi(v);
+    if (forced >= 32) part = forced / 32 * 32;
+  }
   plan->part_tokens = part;
   plan->max_parts = std::max(1, (max_seq_len + part - 1) / part);
   plan->ws_bytes = attn_workspace_bytes(batch, h, plan->max_parts);
+  if (plan->variant == 2) {
+    plan->max_parts = 1;   // no merge kernel: the last CTA of a stream merges it
+    plan->ws_bytes = flat_workspace_bytes(batch, h, kvh);
+  }
   return VT_OK;
 }
 
@@ -150,8 +200,15 @@ int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_strid
   p.k_table = k_table; p.v_table = v_table; p.slot_ids = slot_ids; p.seq_lens = seq_lens;
   p.batch = batch; p.h = h; p.kvh = kvh; p.scale = scale; p.k_scale = k_scale; p.v_scale = v_scale;
   p.lse = lse; p.part_tokens = plan.part_tokens; p.max_parts = plan.max_parts;
-  vt::carve_workspace(workspace, batch, h, plan.max_parts, &p);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (plan.variant == 2) {
+    vt::carve_flat(workspace, batch, kvh, &p);
+    p.n_ctas = vt::flat_grid();
+    if (cudaMemsetAsync(p.fl_count, 0, static_cast<size_t>(batch) * kvh * sizeof(unsigned), s) != cudaSuccess)
+      return VT_ERR_CUDA;
+    return vt::launch_attn_flat(p, kv_dtype, s);
+  }
+  vt::carve_workspace(workspace, batch, h, plan.max_parts, &p);
   int st = plan.variant == 0 ? vt::launch_attn_simt(p, kv_dtype, s) : vt::launch_attn_mma(p, kv_dtype, s);
   if (st != VT_OK) return st;
   if (plan.max_parts > 1) st = vt::launch_attn_reduce(p, kv_dtype, s);

@@ -33,11 +33,19 @@ struct AttnParams {
   uint32_t *status;                   // scratch status word
   float *ws_ml;                       // [batch, h, max_parts, 2]  (max in log2 domain, sum)
   float *ws_o;                        // [batch, h, max_parts, 128] unnormalised partial outputs
+  // flat (persistent) schedule only
+  int n_ctas;                         // grid size
+  unsigned *fl_count;                 // [batch * kv-head slabs] piece tickets, zero between launches
+  float *fl_part;                     // [n_ctas, 2 slots, 4 warps, 8 or 16 heads, 132] piece states
 };
+
+constexpr int kFlatMaxBatch = 2048;   // prefix table of the flat schedule lives in shared memory
+constexpr int kFlatPartRow = 132;     // floats per published piece state row (16-byte aligned)
+constexpr int kFlatMaxCtas = 320;     // 2 per SM on up to 160 SMs
 
 struct AttnPlan {
   int part_tokens, max_parts;
-  int variant;       // 0 = SIMT (one kv head per CTA), 1 = tensor-core GQA
+  int variant;       // 0 = SIMT split-K, 1 = tensor-core split-K, 2 = tensor-core flat schedule
   size_t ws_bytes;
 };
 // Picks the partition size and kernel variant for a problem; num_splits 0 = auto.
@@ -48,6 +56,9 @@ void carve_workspace(void *ws, int batch, int h, int max_parts, AttnParams *p);
 
 int launch_attn_simt(const AttnParams &p, int kv_dtype, cudaStream_t stream);
 int launch_attn_mma(const AttnParams &p, int kv_dtype, cudaStream_t stream);
+bool attn_mma_supports(int h, int kvh, int kv_dtype);
+int launch_attn_flat(const AttnParams &p, int kv_dtype, cudaStream_t stream);
+bool attn_flat_supports(int batch, int h, int kvh, int kv_dtype);
 int launch_attn_reduce(const AttnParams &p, int kv_dtype, cudaStream_t stream);
 
 }  // namespace vt

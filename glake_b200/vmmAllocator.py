@@ -176,6 +176,8 @@ class KVcacheSegment:
 
     def close(self):
         if self._h:
+            for slot in [k for k, (seg, _) in _slot_registry.items() if seg is self]:
+                del _slot_registry[slot]
             check(lib.vt_seg_destroy(self._h), "vt_seg_destroy")
             self._h = None
 

@@ -56,10 +56,17 @@ def test_golden_cases_cache_bits_and_attention(G, oracle, name):
         kv.close()
 
 
-@pytest.mark.parametrize("h,kvh", [(4, 4), (8, 4), (8, 2), (8, 1), (16, 1)])
+@pytest.mark.parametrize("h,kvh", [(4, 4), (8, 4), (8, 2), (8, 1), (16, 1), (32, 8), (12, 12), (3, 3)])
+@pytest.mark.parametrize("mode", ["auto", "simt", "mma", "flat"])
 @pytest.mark.parametrize("splits", [0, 1, 3])
-def test_group_sizes_and_forced_splits(G, oracle, h, kvh, splits):
-    lens = [1, 31, 32, 33, 700, 1300]
+def test_group_sizes_variants_and_forced_splits(G, oracle, monkeypatch, h, kvh, mode, splits):
+    """Every kernel variant (SIMT split-K, tensor-core split-K, tensor-core flat
+    schedule) on every head-group shape, with and without forced partitions."""
+    if mode != "auto":
+        monkeypatch.setenv("VT_ATTN_VARIANT", mode)
+    if mode == "flat" and splits:
+        pytest.skip("the flat schedule has no split count")
+    lens = [1, 31, 32, 33, 700, 1300, 65, 64]
     q, k, v = synth.make_case(100 + h + kvh, lens, h, kvh)
     kv = G.GpuKV(k, v, kvh)
     try:
