@@ -28,6 +28,17 @@
 namespace vt {
 namespace {
 
+#ifdef VT_TRACE
+__device__ __forceinline__ unsigned long long gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define VT_TR(slot) do { if (p.trace && (threadIdx.x & 31) == 0) p.trace[(blockIdx.x * 5 + (threadIdx.x >> 5)) * 8 + (slot)] = gtime(); } while (0)
+#else
+#define VT_TR(slot) do {} while (0)
+#endif
+
 constexpr int kStages = kMmaStages;
 constexpr int kCWarps = kMmaCWarps;
 constexpr int kThreads = kMmaThreads;
@@ -84,6 +95,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
   const int g = p.h / p.kvh;
   const int slabs = p.kvh / HS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  VT_TR(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full0 + 8 * s, 1);
@@ -111,6 +123,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
     if (lane == 0) prefix[0] = 0;
   }
   __syncthreads();
+  VT_TR(1);
   const long long total = prefix[p.batch];
   // Only min(grid, total) CTAs take part, so that every participating CTA owns at
   // least one tile and the piece count of a stream is a plain difference.
@@ -139,6 +152,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
           if (lane == 0) atomicExch(p.status, kKernelErrMagic);
           return;
         }
+        if (it == 0) VT_TR(2);
         const int t0 = tile * TILE_TOK;
         const int nt = min(TILE_TOK, seq_len - t0);
         if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2u * nt * HS * kRowB);
@@ -150,6 +164,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
       }
       tau += pc.tile_end - pc.tile_begin;
     }
+    VT_TR(5);
     return;
   }
 
@@ -186,6 +201,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
       const int s = it % kStages;
       if (!failed && !mbar_wait(full0 + 8 * s, (it / kStages) & 1)) failed = true;
       if (failed) continue;
+      if (it == 0) VT_TR(2);
       const int tok0 = tile * TILE_TOK + rr;      // token of fragment row 0
       if (tok0 < seq_len)
         st.tile(ring0 + s * kStageB, smem + s * kStageB, k_off, v_off, row_off,
@@ -194,6 +210,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
     }
     st.finish_sums();
+    VT_TR(3);
 
     const bool whole = pc.tile_begin == 0 && pc.tile_end == pc.tiles_in_stream;
     if (R == 1 && whole) {
@@ -222,7 +239,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
       // Publish this piece, draw a ticket, and merge the stream if it was the last one.
       const int slot_id = first_piece ? 0 : 1;
       st.template store<kPartRow>(
-          p.fl_part + ((static_cast<size_t>(blockIdx.x) * 2 + slot_id) * kCWarps + warp) * HEADS * kPartRow, lane);
+          p.fl_part + ((static_cast<size_t>(blockIdx.x) * 2 + slot_id) * kCWarps + warp) * HEADS * kPartRow, lane, g);
       __threadfence();
       named_bar_sync(1, kCWarps * 32);
       const long long s_begin = pc.stream_begin, s_end = pc.stream_begin + pc.tiles_in_stream;
@@ -274,14 +291,28 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
             L = L * rescale + ls;
             acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
             M = Mn;
+            // Eight independent 16-byte loads in flight per lane; absent sources carry
+            // weight 0 and re-read the lane's own row (or source 0's), never garbage.
+            const unsigned long long mine_bits = reinterpret_cast<unsigned long long>(mine);
+            const unsigned long long any_bits = __shfl_sync(0xffffffffu, mine_bits, 0);
             const int cnt = min(32, n_src - s0);
-            for (int j = 0; j < cnt; ++j) {
-              const float f = __shfl_sync(0xffffffffu, fi, j);
-              const float *src = reinterpret_cast<const float *>(
-                  __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(mine), j));
-              const float4 v = __ldcg(reinterpret_cast<const float4 *>(src) + lane);
-              acc.x = fmaf(f, v.x, acc.x); acc.y = fmaf(f, v.y, acc.y);
-              acc.z = fmaf(f, v.z, acc.z); acc.w = fmaf(f, v.w, acc.w);
+            for (int j0 = 0; j0 < cnt; j0 += 8) {
+              float f[8];
+              float4 v[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const int j = min(j0 + u, 31);
+                f[u] = __shfl_sync(0xffffffffu, fi, j);
+                unsigned long long bits = __shfl_sync(0xffffffffu, mine_bits, j);
+                if (bits == 0ull) bits = any_bits;
+                v[u] = __ldcg(reinterpret_cast<const float4 *>(bits) + lane);
+              }
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const float w = j0 + u < cnt ? f[u] : 0.f;
+                acc.x = fmaf(w, v[u].x, acc.x); acc.y = fmaf(w, v[u].y, acc.y);
+                acc.z = fmaf(w, v[u].z, acc.z); acc.w = fmaf(w, v[u].w, acc.w);
+              }
             }
           }
           const int hq = (pc.slab * HS + hh) * g + head;
@@ -296,7 +327,9 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
     }
     first_piece = false;
     tau += pc.tile_end - pc.tile_begin;
+    VT_TR(4);
   }
+  VT_TR(5);
   if (failed && lane == 0) atomicExch(p.status, kKernelErrMagic);
 }
 

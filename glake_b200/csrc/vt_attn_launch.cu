@@ -204,6 +204,9 @@ int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_strid
   if (plan.variant == 2) {
     vt::carve_flat(workspace, batch, kvh, &p);
     p.n_ctas = vt::flat_grid();
+#ifdef VT_TRACE
+    p.trace = getenv("VT_TRACE_PTR") ? reinterpret_cast<unsigned long long *>(strtoull(getenv("VT_TRACE_PTR"), nullptr, 0)) : nullptr;
+#endif
     if (cudaMemsetAsync(p.fl_count, 0, static_cast<size_t>(batch) * kvh * sizeof(unsigned), s) != cudaSuccess)
       return VT_ERR_CUDA;
     return vt::launch_attn_flat(p, kv_dtype, s);

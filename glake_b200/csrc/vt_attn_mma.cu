@@ -135,7 +135,7 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(AttnParams p) {
   named_bar_sync(1, kCWarps * 32);   // every consumer is done reading the ring
   constexpr int HEADS = NB * 8;
   float *mbuf = reinterpret_cast<float *>(smem);   // [kCWarps][HEADS][130]
-  st.store<130>(mbuf + warp * HEADS * 130, lane);
+  st.template store<130>(mbuf + warp * HEADS * 130, lane, g);
   named_bar_sync(1, kCWarps * 32);
   if (failed && threadIdx.x == 0) atomicExch(p.status, kKernelErrMagic);
 

@@ -37,6 +37,9 @@ struct AttnParams {
   int n_ctas;                         // grid size
   unsigned *fl_count;                 // [batch * kv-head slabs] piece tickets, zero between launches
   float *fl_part;                     // [n_ctas, 2 slots, 4 warps, 8 or 16 heads, 132] piece states
+#ifdef VT_TRACE
+  unsigned long long *trace;          // debug builds only: per-CTA timestamps
+#endif
 };
 
 constexpr int kFlatMaxBatch = 2048;   // prefix table of the flat schedule lives in shared memory

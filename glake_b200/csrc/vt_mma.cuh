@@ -179,8 +179,9 @@ struct WarpAttn {
   }
 
   // Spill the state as rows of (128 x O, m, l) per q head: dst[head * ROW + ...].
+  // Rows of padding heads (>= g) are skipped.
   template <int ROW>
-  __device__ __forceinline__ void store(float *dst, int lane) const {
+  __device__ __forceinline__ void store(float *dst, int lane, int g) const {
     const int r4 = lane >> 2, c4 = lane & 3;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb) {
@@ -188,16 +189,24 @@ struct WarpAttn {
 #pragma unroll
       for (int mb = 0; mb < 8; ++mb) {
         const int d0 = mb * 16 + r4;
-        dst[h0 * ROW + d0] = o[nb][mb][0];
-        dst[(h0 + 1) * ROW + d0] = o[nb][mb][1];
-        dst[h0 * ROW + d0 + 8] = o[nb][mb][2];
-        dst[(h0 + 1) * ROW + d0 + 8] = o[nb][mb][3];
+        if (h0 < g) {
+          dst[h0 * ROW + d0] = o[nb][mb][0];
+          dst[h0 * ROW + d0 + 8] = o[nb][mb][2];
+        }
+        if (h0 + 1 < g) {
+          dst[(h0 + 1) * ROW + d0] = o[nb][mb][1];
+          dst[(h0 + 1) * ROW + d0 + 8] = o[nb][mb][3];
+        }
       }
       if (r4 == 0) {
-        dst[h0 * ROW + 128] = mrun[nb][0];
-        dst[h0 * ROW + 129] = lrun[nb][0];
-        dst[(h0 + 1) * ROW + 128] = mrun[nb][1];
-        dst[(h0 + 1) * ROW + 129] = lrun[nb][1];
+        if (h0 < g) {
+          dst[h0 * ROW + 128] = mrun[nb][0];
+          dst[h0 * ROW + 129] = lrun[nb][0];
+        }
+        if (h0 + 1 < g) {
+          dst[(h0 + 1) * ROW + 128] = mrun[nb][1];
+          dst[(h0 + 1) * ROW + 129] = lrun[nb][1];
+        }
       }
     }
   }
