@@ -38,6 +38,10 @@ WORKLOADS = {
     #  name       layers  B    H   KVH   lo     hi     fp8
     "7b":       (32,    64,  32, 32,  1024,  4096,  False),
     "70b":      (80,    64,  64, 8,   4096,  16384, False),
+    # one rank's share of the 70b workload at TP = 2 / 4 / 8, runnable on a single GPU (tuning)
+    "70b-tp2":  (80,    64,  32, 4,   4096,  16384, False),
+    "70b-tp4":  (80,    64,  16, 2,   4096,  16384, False),
+    "70b-tp8":  (80,    64,  8,  1,   4096,  16384, False),
     "op1":      (1,     8,   32, 32,  512,   2048,  False),
     "gqa-long": (1,     32,  32, 8,   16384, 32768, False),
     "gqa-fp8":  (1,     128, 32, 8,   2048,  8192,  True),
@@ -45,6 +49,9 @@ WORKLOADS = {
 WORKLOAD_TEXT = {
     "7b": "llama2-7b-shape decode step: 32 layers x (KV append + decode attention), batch 64, 32/32 heads, ctx U[1k,4k]",
     "70b": "llama3-70b-shape decode step, heads sharded over ranks: 80 layers x (KV append + decode attention), batch 64, 64/8 heads, ctx U[4k,16k]",
+    "70b-tp2": "one rank's share (32/4 heads) of the llama3-70b-shape decode step at TP=2, on one GPU",
+    "70b-tp4": "one rank's share (16/2 heads) of the llama3-70b-shape decode step at TP=4, on one GPU",
+    "70b-tp8": "one rank's share (8/1 heads) of the llama3-70b-shape decode step at TP=8, on one GPU",
     "op1": "decode attention op, batch 8, 32/32 heads, ctx U[512,2048]",
     "gqa-long": "llama3-8b-shape GQA decode attention op, batch 32, 32/8 heads, ctx U[16k,32k]",
     "gqa-fp8": "llama3-8b-shape GQA decode attention op, fp8 e4m3 KV, batch 128, 32/8 heads, ctx U[2k,8k]",
@@ -147,7 +154,7 @@ class Job:
         chunk = A.granularitySize
         need = sum(((n + total_steps) * row + chunk - 1) // chunk for n in self.lens) * 2 * layers
         t0 = time.time()
-        if not A.init_physical_handle(need + 2 * layers * 4, self.dev.index):
+        if not A.init_physical_handle(need + 2 * layers * (b + 4), self.dev.index):   # + one look-ahead chunk per slot
             raise RuntimeError("chunk pool creation failed")
         self.engine = VTensorCacheEngine(layers, self.kvh, D, b, hi + total_steps + 8, cache_dtype=self.dtype)
         self.impl = VTensorAttentionImpl(self.h, D, D ** -0.5, self.kvh, kv_cache_dtype=self.dtype)
@@ -174,83 +181,79 @@ class Job:
         torch.cuda.synchronize()
         self.setup_s = time.time() - t0
         # per-step inputs: one set per layer, reused every step (values do not matter for timing)
-        self.q = torch.randn(layers, b, self.h * D, device=self.dev, dtype=torch.bfloat16, generator=gen)
-        self.k = torch.randn(layers, b, self.kvh * D, device=self.dev, dtype=torch.bfloat16, generator=gen)
-        self.v = torch.randn(layers, b, self.kvh * D, device=self.dev, dtype=torch.bfloat16, generator=gen)
-        self.hq = self.q.cpu().pin_memory()
-        self.hk = self.k.cpu().pin_memory()
-        self.hv = self.v.cpu().pin_memory()
-        self.hout = torch.empty(layers, b, self.h * D, dtype=torch.bfloat16).pin_memory()
+        from glake_b200.backend import DecodeRunner
+        sk = self.scale_k if fp8 else None
+        sv = self.scale_v if fp8 else None
+        self.resident = DecodeRunner(self.engine, self.impl, b, host_io=False, k_scale=sk, v_scale=sv)
+        self.hostio = DecodeRunner(self.engine, self.impl, b, host_io=True, k_scale=sk, v_scale=sv)
+        for t in (self.resident.q, self.resident.k, self.resident.v):
+            t.copy_(torch.randn(t.shape, device=self.dev, dtype=torch.bfloat16, generator=gen))
+        self.hostio.hq.copy_(self.resident.q)
+        self.hostio.hk.copy_(self.resident.k)
+        self.hostio.hv.copy_(self.resident.v)
+        torch.cuda.synchronize()
         self.launches = 0
         self.num_splits = args.num_splits
 
     def _meta(self):
-        """Advance every sequence by one token and do the step's allocator work."""
+        """Advance every sequence by one token; the scheduler's part of the step."""
         row = self.kvh * D * self.e
         self.lens = [n + 1 for n in self.lens]
         extend = []
         for slot, seg in zip(self.slots, self.engine.vmm_kvcache_segment):
             # the scheduler's rule: ask for the next chunk one row before it is needed
-            extend.append(slot if seg.used_size + 2 * row > seg.actual_size else -1)
-        meta = self.VTensorMetadata(self.slots, self.lens, self.kvh, D, num_decode_tokens=self.b,
+            extend.append(slot if seg.used_size + 2 * row > seg.actual_size and seg.ready() else -1)
+        return self.VTensorMetadata(self.slots, self.lens, self.kvh, D, num_decode_tokens=self.b,
                                     extend_seq_list=extend, kv_elem_size=self.e)
-        return self.prepare_step(meta, self.engine)
-
-    def _layers(self, meta, q, k, v, out=None):
-        from glake_b200 import ops
-        _, parts, _ = ops.attn_plan(self.b, self.h, self.kvh, meta.max_seq_len, self.dtype, self.num_splits)
-        for layer in range(self.layers):
-            kc, vc = self.engine.gpu_cache[layer]
-            o = self.impl.forward(q[layer], k[layer], v[layer], kc, vc, meta,
-                                  k_scale=self.scale_k[layer] if self.fp8 else None,
-                                  v_scale=self.scale_v[layer] if self.fp8 else None)
-            if out is not None:
-                out[layer].copy_(o, non_blocking=True)
-            self.launches += 2 + (1 if parts > 1 else 0)
 
     def step_resident(self):
-        self._layers(self._meta(), self.q, self.k, self.v)
+        self.resident.step(self._meta())
+        self.launches += self.resident.kernel_launches_per_step
 
     def step_e2e(self):
         """Host buffers in, host buffer out: pinned q/k/v for every layer are copied
         to the device inside the step and the attention outputs are copied back."""
-        meta = self._meta()
-        q = self.hq.to(self.dev, non_blocking=True)
-        k = self.hk.to(self.dev, non_blocking=True)
-        v = self.hv.to(self.dev, non_blocking=True)
-        self._layers(meta, q, k, v, self.hout)
+        self.hostio.step(self._meta())
+        self.launches += self.hostio.kernel_launches_per_step
+
+    def streams(self):
+        return [self.resident.stream, self.hostio.stream]
 
     def time_attention_only(self, iters=3):
-        """CUDA-event time of the decode-attention call alone (attention kernel +
-        merge kernel), averaged over layers x iters, for the roofline."""
+        """CUDA-event time of the decode-attention call alone (one layer's launch),
+        averaged over layers x iters, for the roofline.  A spin kernel is queued
+        first so that every timed launch is already waiting in the stream when the
+        GPU reaches it (otherwise host launch latency would be counted)."""
         torch = self.torch
         from glake_b200 import ops
-        meta = self.VTensorMetadata(self.slots, self.lens, self.kvh, D, num_decode_tokens=self.b, kv_elem_size=self.e)
-        segs = [self.engine.vmm_kvcache_segment[s] for s in self.slots]
-        meta.slot_mapping = torch.tensor(self.slots, dtype=torch.int64, device=self.dev)
-        meta.seq_lens_tensor = torch.tensor(self.lens, dtype=torch.int32, device=self.dev)
-        meta.max_seq_len = max(self.lens)
+        sl = torch.tensor(self.lens, dtype=torch.int32, device=self.dev)
+        sm = torch.tensor(self.slots, dtype=torch.int64, device=self.dev)
+        mx = max(self.lens)
         out = torch.empty(self.b, self.h, D, dtype=torch.bfloat16, device=self.dev)
+        q = self.resident.q
         evs = []
+        torch.cuda.synchronize()
         for it in range(iters + 1):
+            torch.cuda._sleep(int(4e6 + 1e5 * self.layers))
             for layer in range(self.layers):
                 kc, vc = self.engine.gpu_cache[layer]
                 a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record()
-                ops.paged_attention_v1(out, self.q[layer].view(self.b, self.h, D), kc.vmm_ptr, vc.vmm_ptr, self.kvh,
-                                       D ** -0.5, meta.seq_lens_tensor, 1, meta.max_seq_len, None, self.dtype, 1.0,
-                                       meta.slot_mapping,
+                ops.paged_attention_v1(out, q[layer].view(self.b, self.h, D), kc.vmm_ptr, vc.vmm_ptr, self.kvh,
+                                       D ** -0.5, sl, 1, mx, None, self.dtype, 1.0, sm,
                                        k_scale=self.scale_k[layer] if self.fp8 else None,
                                        v_scale=self.scale_v[layer] if self.fp8 else None, num_splits=self.num_splits)
                 z.record()
                 if it > 0:
                     evs.append((a, z))
-        torch.cuda.synchronize()
+            torch.cuda.synchronize()
         ms = [a.elapsed_time(z) for a, z in evs]
         return sum(ms) / len(ms)
 
 
-def timed(job, fn, steps, warmup, world):
+def timed(job, fn, stream, steps, warmup, world):
+    """W warm-up steps, barrier + synchronize, K timed steps bracketed by CUDA events
+    on the stream the graphs replay on, synchronize, max over ranks."""
     import torch
     import torch.distributed as dist
     for _ in range(warmup):
@@ -262,10 +265,10 @@ def timed(job, fn, steps, warmup, world):
     lens0 = list(job.lens)
     job.launches = 0
     a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record()
+    a.record(stream)
     for _ in range(steps):
         fn()
-    z.record()
+    z.record(stream)
     torch.cuda.synchronize()
     ms = a.elapsed_time(z)
     if world > 1:
@@ -300,18 +303,18 @@ def run_ours(args):
     job = Job(args, name, rank, world)
 
     sampler = ClockSampler(local) if rank == 0 else None
-    ms, attn_b, app_b, launches = timed(job, job.step_resident, args.steps, args.warmup, world)
+    ms, attn_b, app_b, launches = timed(job, job.step_resident, job.resident.stream, args.steps, args.warmup, world)
     clocks = sampler.stop() if sampler else None
     attn_ms = job.time_attention_only()
     lens_now = list(job.lens)
     e2e = None
     if not args.no_e2e:
-        ms2, attn2, app2, _ = timed(job, job.step_e2e, args.steps, args.warmup, world)
+        ms2, attn2, app2, _ = timed(job, job.step_e2e, job.hostio.stream, args.steps, args.warmup, world)
         per_layer_in = b * (job.h + 2 * job.kvh) * D * 2
         e2e = {"value": round((attn2 + app2) * world / (ms2 * 1e-3) / 1e9, 2), "unit": "GB/s",
                "ms_per_step": round(ms2 / args.steps, 4),
                "tokens_per_s": round(b * args.steps / (ms2 * 1e-3), 1),
-               "h2d_bytes_per_step": world * (job.layers * per_layer_in + 4 * b * 8),
+               "h2d_bytes_per_step": world * (job.layers * per_layer_in + b * 24),
                "d2h_bytes_per_step": world * job.layers * b * job.h * D * 2}
     status = __import__("glake_b200.ops", fromlist=["attn_status"]).attn_status()
     if rank != 0:
@@ -346,8 +349,8 @@ def run_ours(args):
                    "q_heads_per_gpu": job.h, "kv_heads_per_gpu": job.kvh, "head_dim": D,
                    "context_mean_at_end": round(sum(lens_now) / b, 1), "seed": args.seed,
                    "l2": "inputs larger than L2: each layer streams its own KV ranges (>= 1 GiB per layer-op), no flush needed",
-                   "split_k": {"part_tokens": part, "max_parts": parts, "variant": "simt" if variant == 0 else "mma"},
-                   "kv_setup_seconds": round(job.setup_s, 1), "parallelism": f"tp{world} (heads sharded, no collective in the path)"},
+                   "split_k": {"part_tokens": part, "max_parts": parts, "variant": ["simt split-k", "tensor-core split-k", "tensor-core flat persistent"][variant]},
+                   "kv_setup_seconds": round(job.setup_s, 1), "cuda_graph": True, "parallelism": f"tp{world} (heads sharded, no collective in the path)"},
         "tokens_per_s": round(b * args.steps / (ms * 1e-3), 1),
         "pct_of_nominal_8TBs": round(100 * achieved / 8000.0, 1),
         "gpu_launches": launches,

@@ -96,11 +96,10 @@ class VTensorMetadata:
     kvcache_segment: Optional[list] = None
 
 
-def prepare_step(meta: VTensorMetadata, engine: VTensorCacheEngine, device=None):
-    """Allocator work of one model step, before the layer loop (llama.py:307-341):
-    wait (bounded) for growths that this step needs, queue the next ones, obtain
-    each entry's byte offset, upload the small per-step tensors."""
-    device = device or engine.device
+def prepare_step_host(meta: VTensorMetadata, engine: VTensorCacheEngine):
+    """Host half of the allocator work of one model step (llama.py:307-341): wait
+    (bounded) for growths this step needs, queue the next ones, obtain each entry's
+    byte offset.  Returns (byte offsets, source-row starts) as Python lists."""
     slots = meta.slot_mapping_list
     segs = [engine.vmm_kvcache_segment[s] for s in slots]
     meta.kvcache_segment = segs
@@ -121,19 +120,27 @@ def prepare_step(meta: VTensorMetadata, engine: VTensorCacheEngine, device=None)
         kv_size_list = [n * kv_size for n in rows]
     set_used = meta.set_used_size if meta.set_used_size is not None else [0] * len(slots)
     slot_m = vmmAllocator.extend_kv_cache_batch(None, None, slots, kv_size_list, segs, set_used, kv_size, decode)
-    # one small pinned staging buffer -> one H2D copy for all per-step integers
-    n = len(slots)
     starts, acc = [], 0
     for r in rows:
         starts.append(acc)
         acc += r
+    meta.max_seq_len = max(meta.seq_lens) if meta.seq_lens else 0
+    return slot_m, starts
+
+
+def prepare_step(meta: VTensorMetadata, engine: VTensorCacheEngine, device=None):
+    """prepare_step_host plus the upload of the small per-step tensors (the
+    reference's ``torch.tensor(slot_m, device="cuda")``, llama.py:341) in one copy."""
+    device = device or engine.device
+    slot_m, starts = prepare_step_host(meta, engine)
+    slots = meta.slot_mapping_list
+    n = len(slots)
     host = torch.tensor(slot_m + list(slots) + list(meta.seq_lens) + starts, dtype=torch.int64).pin_memory()
     dev = host.to(device, non_blocking=True)
     meta.slot_m = dev[:n]
     meta.slot_mapping = dev[n:2 * n]
     meta.seq_lens_tensor = dev[2 * n:3 * n].to(torch.int32)
     meta.cache_seq_lens = dev[3 * n:4 * n].to(torch.int32)
-    meta.max_seq_len = max(meta.seq_lens) if meta.seq_lens else 0
     return meta
 
 
@@ -166,3 +173,101 @@ class VTensorAttentionImpl:
                                     m.seq_lens_tensor, None, None, None, None, None, None, self.scale, True, -1, -1,
                                     None, 4, kv_cache_dtype=self.kv_cache_dtype, k_scale=k_scale, v_scale=v_scale)
         return output.view(-1, self.num_heads * self.head_size)
+
+
+class DecodeRunner:
+    """One decode step of the hot path over all layers, replayed as a CUDA graph.
+
+    The reference captures its decode step in CUDA graphs as well
+    (GLakeServe/vllm/worker/model_runner.py:782-930); what makes that possible on
+    the vTensor layout is that a slot's K/V base addresses never change while it
+    grows, so a captured kernel stays valid across steps.  Per step the host only
+    does the allocator bookkeeping (and maps chunks when a sequence crosses a
+    2 MiB boundary), writes ~24 bytes per sequence into a pinned staging buffer and
+    replays.  ``host_io=True`` adds the copies of pinned host q/k/v to the device
+    and of the outputs back to pinned host memory to the graph.
+    """
+
+    BUCKET = 2048  # graphs are keyed by max context rounded up to this many tokens
+
+    def __init__(self, engine: VTensorCacheEngine, impl: VTensorAttentionImpl, batch, host_io=False,
+                 k_scale=None, v_scale=None):
+        self.engine, self.impl, self.batch, self.host_io = engine, impl, batch, host_io
+        self.k_scale, self.v_scale = k_scale, v_scale
+        dev, layers = engine.device, engine.num_layers
+        hd, kd = impl.num_heads * impl.head_size, impl.num_kv_heads * impl.head_size
+        self.q = torch.zeros(layers, batch, hd, dtype=torch.bfloat16, device=dev)
+        self.k = torch.zeros(layers, batch, kd, dtype=torch.bfloat16, device=dev)
+        self.v = torch.zeros(layers, batch, kd, dtype=torch.bfloat16, device=dev)
+        self.out = torch.zeros(layers, batch, hd, dtype=torch.bfloat16, device=dev)
+        self.h64 = torch.zeros(2 * batch, dtype=torch.int64).pin_memory()     # byte offsets | slot ids
+        self.h32 = torch.zeros(2 * batch, dtype=torch.int32).pin_memory()     # seq lens | source-row starts
+        self.d64 = torch.zeros(2 * batch, dtype=torch.int64, device=dev)
+        self.d32 = torch.zeros(2 * batch, dtype=torch.int32, device=dev)
+        if host_io:
+            self.hq, self.hk, self.hv = (torch.zeros_like(t, device="cpu").pin_memory() for t in (self.q, self.k, self.v))
+            self.hout = torch.zeros_like(self.out, device="cpu").pin_memory()
+        self.graphs = {}
+        self.kernel_launches_per_step = 0
+        self.stream = torch.cuda.Stream(device=dev)
+
+    def _body(self, meta):
+        """Everything the device does in one step, on the current stream."""
+        self.d64.copy_(self.h64, non_blocking=True)
+        self.d32.copy_(self.h32, non_blocking=True)
+        if self.host_io:
+            self.q.copy_(self.hq, non_blocking=True)
+            self.k.copy_(self.hk, non_blocking=True)
+            self.v.copy_(self.hv, non_blocking=True)
+        b = self.batch
+        for layer in range(self.engine.num_layers):
+            kc, vc = self.engine.gpu_cache[layer]
+            ks = self.k_scale[layer] if self.k_scale is not None else None
+            vs = self.v_scale[layer] if self.v_scale is not None else None
+            ops.reshape_and_cache(self.k[layer], self.v[layer], self.engine.k_cache_ptr[layer],
+                                  self.engine.v_cache_ptr[layer], self.d64[:b], self.d64[b:], self.d32[:b],
+                                  self.d32[b:], 1, self.impl.num_kv_heads, self.impl.head_size,
+                                  self.impl.kv_cache_dtype, ks, vs)
+            ops.paged_attention_v1(self.out[layer].view(b, self.impl.num_heads, self.impl.head_size),
+                                   self.q[layer].view(b, self.impl.num_heads, self.impl.head_size), kc.vmm_ptr,
+                                   vc.vmm_ptr, self.impl.num_kv_heads, self.impl.scale, self.d32[:b], 1,
+                                   meta.max_seq_len, None, self.impl.kv_cache_dtype, 1.0, self.d64[b:],
+                                   k_scale=ks, v_scale=vs)
+        if self.host_io:
+            self.hout.copy_(self.out, non_blocking=True)
+
+    def step(self, meta: VTensorMetadata):
+        """Runs one decode step for ``meta`` (slot ids and context lengths as lists).
+        Inputs are whatever ``self.q/k/v`` (or ``self.hq/hk/hv``) hold; outputs land
+        in ``self.out`` (or ``self.hout``).  Asynchronous: returns after the replay
+        has been enqueued on ``self.stream``."""
+        assert len(meta.slot_mapping_list) == self.batch
+        slot_m, starts = prepare_step_host(meta, self.engine)
+        b = self.batch
+        self.stream.synchronize()   # the previous replay may still be reading the staging buffers
+        self.h64[:b] = torch.tensor(slot_m, dtype=torch.int64)
+        self.h64[b:] = torch.tensor(meta.slot_mapping_list, dtype=torch.int64)
+        self.h32[:b] = torch.tensor(meta.seq_lens, dtype=torch.int32)
+        self.h32[b:] = torch.tensor(starts, dtype=torch.int32)
+        bucket = (meta.max_seq_len + self.BUCKET - 1) // self.BUCKET * self.BUCKET
+        graph = self.graphs.get(bucket)
+        if graph is None:
+            capture_meta = VTensorMetadata(meta.slot_mapping_list, meta.seq_lens, meta.kv_num_heads,
+                                           meta.kv_head_size, kv_elem_size=meta.kv_elem_size)
+            capture_meta.max_seq_len = bucket
+            with torch.cuda.stream(self.stream):
+                self._body(capture_meta)        # warm-up outside capture (sets kernel attributes)
+                self.stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=self.stream):
+                    self._body(capture_meta)
+            self.graphs[bucket] = graph
+            _, parts, _ = ops.attn_plan(b, self.impl.num_heads, self.impl.num_kv_heads, bucket,
+                                        self.impl.kv_cache_dtype)
+            self.kernel_launches_per_step = self.engine.num_layers * (2 + (1 if parts > 1 else 0))
+            return  # the warm-up pass above already executed this step
+        with torch.cuda.stream(self.stream):
+            graph.replay()
+
+    def synchronize(self):
+        self.stream.synchronize()
