@@ -13,6 +13,8 @@ LIB_PATH = os.path.join(_HERE, "libvtensor.so")
 VT_OK = 0
 VT_ERR_INVALID, VT_ERR_DRIVER, VT_ERR_POOL_EMPTY, VT_ERR_RESERVE, VT_ERR_TIMEOUT = 1, 2, 3, 4, 5
 VT_ERR_UNSUPPORTED, VT_ERR_CUDA, VT_ERR_STATE, VT_ERR_NO_DRIVER, VT_ERR_KERNEL = 6, 7, 8, 9, 10
+VT_ERR_TOO_LARGE = 11
+VT_STATIC_SCRATCH_BYTES = 12 << 20
 VT_KV_BF16, VT_KV_FP8_E4M3 = 0, 1
 
 
@@ -76,6 +78,8 @@ def _load():
         "vt_decode_attn_workspace_bytes": (c_int, [c_int, c_int, c_int, c_int, POINTER(sz)]),
         "vt_decode_attn": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                                    c_float, c_int, vp, vp, vp, vp, sz, c_int, vp]),
+        "vt_decode_attn_static": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
+                                          c_float, c_int, vp, vp, vp, c_int, vp]),
         "vt_decode_attn_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int),
                                         POINTER(c_int)]),
         "vt_decode_attn_status": (c_int, [vp, vp, POINTER(c_int)]),

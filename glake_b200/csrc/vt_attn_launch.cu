@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 #include "../../include/vtensor.h"
 #include "vt_device.cuh"
@@ -218,6 +219,51 @@ int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_strid
   return st;
 }
 
+}  // extern "C"
+
+// Scratch of vt_decode_attn_static.  In host code the name below is only a
+// stand-in for the symbol, not a device address: the address is looked up once
+// per device with cudaGetSymbolAddress and that pointer is what kernels receive.
+static __device__ __align__(256) unsigned char g_static_scratch[VT_STATIC_SCRATCH_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void *g_static_ptr[64] = {nullptr};
+
+// Device address of g_static_scratch on the current device (nullptr on failure).
+void *static_scratch_for_current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> g(g_static_mu);
+  if (!g_static_ptr[dev]) {
+    void *ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_static_scratch) != cudaSuccess) return nullptr;
+    g_static_ptr[dev] = ptr;
+  }
+  return g_static_ptr[dev];
+}
+}  // namespace
+
+extern "C" {
+
+int vt_decode_attn_static(void *out, int64_t out_stride, const void *q, int64_t q_stride,
+                          const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
+                          const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len,
+                          float scale, int kv_dtype, const float *k_scale, const float *v_scale,
+                          float *lse, int num_splits, void *stream) {
+  if (batch < 0 || h <= 0 || kvh <= 0 || max_seq_len < 0 || num_splits < 0) return VT_ERR_INVALID;
+  if (batch == 0) return VT_OK;
+  if (d != vt::kHeadDim || h % kvh != 0) return VT_ERR_UNSUPPORTED;
+  vt::AttnPlan plan;
+  vt::plan_attn(batch, h, kvh, std::max(max_seq_len, 1), kv_dtype, num_splits, &plan);
+  if (plan.ws_bytes > VT_STATIC_SCRATCH_BYTES) return VT_ERR_TOO_LARGE;
+  void *scratch = static_scratch_for_current_device();
+  if (!scratch) return VT_ERR_CUDA;
+  return vt_decode_attn(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, batch, h, kvh, d,
+                        max_seq_len, scale, kv_dtype, k_scale, v_scale, lse, scratch, VT_STATIC_SCRATCH_BYTES,
+                        num_splits, stream);
+}
+
 int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits,
                         int *part_tokens, int *max_parts, int *variant) {
   if (batch < 0 || h <= 0 || kvh <= 0 || h % kvh != 0 || max_seq_len < 0 || num_splits < 0) return VT_ERR_INVALID;
@@ -254,6 +300,7 @@ const char *vt_strerror(int status) {
     case VT_ERR_STATE: return "call not valid in the current state";
     case VT_ERR_NO_DRIVER: return "libcuda.so.1 could not be loaded";
     case VT_ERR_KERNEL: return "a kernel's bounded wait ran out";
+    case VT_ERR_TOO_LARGE: return "problem needs more scratch than the built-in static buffer holds";
     default: return "unknown status";
   }
 }

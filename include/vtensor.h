@@ -40,7 +40,8 @@ enum {
   VT_ERR_CUDA = 7,         /* kernel launch or runtime call failed */
   VT_ERR_STATE = 8,        /* call not valid in the object's current state */
   VT_ERR_NO_DRIVER = 9,    /* libcuda could not be loaded (no GPU on this machine) */
-  VT_ERR_KERNEL = 10       /* a kernel reported a bounded wait that ran out */
+  VT_ERR_KERNEL = 10,      /* a kernel reported a bounded wait that ran out */
+  VT_ERR_TOO_LARGE = 11    /* problem needs more scratch than the built-in buffer of vt_decode_attn_static */
 };
 
 /* Human-readable text for a status code (static storage). */
@@ -228,6 +229,40 @@ int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_strid
  * Introspection for benchmarks and tests; no counterpart in the reference. */
 int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits,
                         int *part_tokens, int *max_parts, int *variant);
+
+/* vt_decode_attn for callers that cannot allocate device memory at all.
+ * (No counterpart in the reference: its attention ops get their scratch from
+ * torch's allocator.)
+ *
+ * Some hosts of this library have no way to obtain the scratch buffer that
+ * vt_decode_attn asks for: a plugin running inside another runtime's callback
+ * where cudaMalloc is forbidden (it may synchronise the device or deadlock on the
+ * host runtime's allocator lock), a process whose memory budget is fixed at start
+ * and policed, or code that must stay free of allocator calls on its hot path.
+ * For them the split-K / piece scratch lives inside the library, in one
+ * file-scope __device__ array of VT_STATIC_SCRATCH_BYTES bytes that every GPU
+ * holds from the moment it loads the library until the process exits.
+ *
+ * Same arguments and results as vt_decode_attn minus workspace / workspace_bytes;
+ * outputs are identical to vt_decode_attn's for the same inputs.  Differences:
+ *   - a problem whose scratch need exceeds VT_STATIC_SCRATCH_BYTES returns
+ *     VT_ERR_TOO_LARGE and launches nothing (query group of 16, very large
+ *     batch x kv-head counts, or the fp8 split-K path with long contexts);
+ *   - the call itself never allocates or frees: no cudaMalloc / cudaFree and no
+ *     allocating library routine;
+ *   - the FIRST call on each device resolves the array's device address
+ *     (cudaGetSymbolAddress with that device current) and remembers it; make that
+ *     first call before any stream capture begins;
+ *   - all calls on a device share the one array and it keeps the previous call's
+ *     contents (the ticket counters are cleared on every call).  Two calls that
+ *     overlap on the GPU (different streams) race on it: serialise them;
+ *   - the kernel status word of this buffer cannot be read back. */
+#define VT_STATIC_SCRATCH_BYTES (12u << 20)
+int vt_decode_attn_static(void *out, int64_t out_stride, const void *q, int64_t q_stride,
+                          const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
+                          const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len,
+                          float scale, int kv_dtype, const float *k_scale, const float *v_scale,
+                          float *lse, int num_splits, void *stream);
 
 /* Reads (synchronously, on `stream`) the error word the attention kernels set
  * when one of their bounded waits ran out: *code = 0 or VT_ERR_KERNEL. */
