@@ -90,17 +90,27 @@ def algorithmic_bytes(lens, layers, h, kvh, e):
 # clocks
 # ----------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """nvidia-smi sampled every 50 ms in a child process; only samples whose
+    timestamp falls inside [mark_begin, mark_end] (the timed region) are kept."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.proc = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+        self.t0 = self.t1 = None
+
+    def mark_begin(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def stop(self):
         if self.proc is None:
@@ -111,22 +121,29 @@ class ClockSampler:
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        sm, mx, reasons = [], None, set()
+        import datetime
+        sm, sm_all, mx, reasons = [], [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 6:
+            if len(parts) < 7:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx = float(parts[1])
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk = float(parts[1])
+                mx = float(parts[2])
             except ValueError:
                 continue
-            for name, v in zip(names, parts[2:6]):
+            sm_all.append(clk)
+            if self.t0 is not None and self.t1 is not None and not (self.t0 - 0.05 <= ts <= self.t1 + 0.05):
+                continue
+            sm.append(clk)
+            for name, v in zip(names, parts[3:7]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+        use = sm if sm else sm_all
+        return {"sm_mhz": statistics.median(use) if use else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm), "samples_total": len(sm_all)}
 
 
 # ----------------------------------------------------------------------------
@@ -251,7 +268,7 @@ class Job:
         return sum(ms) / len(ms)
 
 
-def timed(job, fn, stream, steps, warmup, world):
+def timed(job, fn, stream, steps, warmup, world, sampler=None):
     """W warm-up steps, barrier + synchronize, K timed steps bracketed by CUDA events
     on the stream the graphs replay on, synchronize, max over ranks."""
     import torch
@@ -265,17 +282,20 @@ def timed(job, fn, stream, steps, warmup, world):
     lens0 = list(job.lens)
     job.launches = 0
     a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if sampler:
+        sampler.mark_begin()
     a.record(stream)
     for _ in range(steps):
         fn()
     z.record(stream)
     torch.cuda.synchronize()
+    if sampler:
+        sampler.mark_end()
     ms = a.elapsed_time(z)
     if world > 1:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        from glake_b200 import tp
+        ms = tp.max_over_ranks(ms, device="cuda")
         dist.barrier()
-        ms = float(t.item())
     # bytes of the timed steps: contexts grow by one per step
     attn = app = 0
     for s in range(steps):
@@ -303,7 +323,8 @@ def run_ours(args):
     job = Job(args, name, rank, world)
 
     sampler = ClockSampler(local) if rank == 0 else None
-    ms, attn_b, app_b, launches = timed(job, job.step_resident, job.resident.stream, args.steps, args.warmup, world)
+    ms, attn_b, app_b, launches = timed(job, job.step_resident, job.resident.stream, args.steps, args.warmup, world,
+                                        sampler)
     clocks = sampler.stop() if sampler else None
     attn_ms = job.time_attention_only()
     lens_now = list(job.lens)
