@@ -352,7 +352,7 @@ def run_ours(args):
     peak = float(peaks.get("hbm_gbs", 6650.0))
     per_launch_attn, _ = algorithmic_bytes(lens_now, 1, job.h, job.kvh, job.e)
     achieved = per_launch_attn / (attn_ms * 1e-3) / 1e9
-    traffic = load_traffic(name)
+    traffic = load_traffic(name, per_launch_attn)
     from glake_b200 import ops
     part, parts, variant = ops.attn_plan(b, job.h, job.kvh, max(lens_now), job.dtype, args.num_splits)
     line = {
@@ -392,13 +392,15 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def load_traffic(name):
-    """DRAM bytes per attention launch from the committed ncu summary, if one
-    exists for this workload (profiles/traffic.json), else null."""
+def load_traffic(name, algorithmic_bytes_per_launch):
+    """DRAM bytes per attention launch: the traffic / algorithmic ratio of the
+    committed ncu capture for this kernel (profiles/traffic.json, taken on a small
+    case; traffic grows in proportion to the tokens read) times this launch's
+    algorithmic bytes.  null when no capture covers the workload."""
     try:
-        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
-        return t.get(name)
-    except (OSError, ValueError):
+        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))).get(name)
+        return int(t["ratio"] * algorithmic_bytes_per_launch) if t else None
+    except (OSError, ValueError, KeyError, TypeError):
         return None
 
 
