@@ -78,6 +78,8 @@ def _load():
         "vt_decode_attn_workspace_bytes": (c_int, [c_int, c_int, c_int, c_int, POINTER(sz)]),
         "vt_decode_attn": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                                    c_float, c_int, vp, vp, vp, vp, sz, c_int, vp]),
+        "vt_decode_step": (c_int, [vp, c_int64, vp, c_int64, vp, vp, c_int64, c_int64, vp, vp, vp, vp, vp, c_int, c_int,
+                                   c_int, c_int, c_int, c_float, c_int, vp, vp, vp, vp, sz, vp]),
         "vt_decode_attn_static": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                                           c_float, c_int, vp, vp, vp, c_int, vp]),
         "vt_decode_attn_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int),

@@ -164,14 +164,12 @@ class VTensorAttentionImpl:
         m = attn_metadata
         if m.num_prefills > 0:
             raise NotImplementedError("prefill goes through glake_b200.prefill")
-        layer = key_cache.layer_index
-        ops.reshape_and_cache(key, value, m.k_cache_segment_ptr_list[layer], m.v_cache_segment_ptr_list[layer],
-                              m.slot_m, m.slot_mapping, m.seq_lens_tensor, m.cache_seq_lens, 1,
-                              self.num_kv_heads, self.head_size, self.kv_cache_dtype, k_scale, v_scale)
-        output, _ = ops.fwd_kvcache(query.unsqueeze(1), key_cache.vmm_ptr, value_cache.vmm_ptr, m.max_seq_len,
-                                    self.num_kv_heads, m.slot_mapping.size(0), m.slot_mapping, None, None,
-                                    m.seq_lens_tensor, None, None, None, None, None, None, self.scale, True, -1, -1,
-                                    None, 4, kv_cache_dtype=self.kv_cache_dtype, k_scale=k_scale, v_scale=v_scale)
+        # append + attention of the layer as one fused step (one kernel launch for a
+        # bf16 cache); equivalent to ops.reshape_and_cache followed by ops.fwd_kvcache
+        output = torch.empty_like(query)
+        ops.decode_step(output, query, key, value, key_cache.vmm_ptr, value_cache.vmm_ptr, m.slot_m, m.slot_mapping,
+                        m.seq_lens_tensor, m.max_seq_len, self.num_kv_heads, self.scale, self.kv_cache_dtype,
+                        k_scale, v_scale)
         return output.view(-1, self.num_heads * self.head_size)
 
 
@@ -224,15 +222,11 @@ class DecodeRunner:
             kc, vc = self.engine.gpu_cache[layer]
             ks = self.k_scale[layer] if self.k_scale is not None else None
             vs = self.v_scale[layer] if self.v_scale is not None else None
-            ops.reshape_and_cache(self.k[layer], self.v[layer], self.engine.k_cache_ptr[layer],
-                                  self.engine.v_cache_ptr[layer], self.d64[:b], self.d64[b:], self.d32[:b],
-                                  self.d32[b:], 1, self.impl.num_kv_heads, self.impl.head_size,
-                                  self.impl.kv_cache_dtype, ks, vs)
-            ops.paged_attention_v1(self.out[layer].view(b, self.impl.num_heads, self.impl.head_size),
-                                   self.q[layer].view(b, self.impl.num_heads, self.impl.head_size), kc.vmm_ptr,
-                                   vc.vmm_ptr, self.impl.num_kv_heads, self.impl.scale, self.d32[:b], 1,
-                                   meta.max_seq_len, None, self.impl.kv_cache_dtype, 1.0, self.d64[b:],
-                                   k_scale=ks, v_scale=vs)
+            ops.decode_step(self.out[layer].view(b, self.impl.num_heads, self.impl.head_size),
+                            self.q[layer].view(b, self.impl.num_heads, self.impl.head_size), self.k[layer],
+                            self.v[layer], kc.vmm_ptr, vc.vmm_ptr, self.d64[:b], self.d64[b:], self.d32[:b],
+                            meta.max_seq_len, self.impl.num_kv_heads, self.impl.scale, self.impl.kv_cache_dtype,
+                            ks, vs)
         if self.host_io:
             self.hout.copy_(self.out, non_blocking=True)
 
@@ -262,9 +256,11 @@ class DecodeRunner:
                 with torch.cuda.graph(graph, stream=self.stream):
                     self._body(capture_meta)
             self.graphs[bucket] = graph
-            _, parts, _ = ops.attn_plan(b, self.impl.num_heads, self.impl.num_kv_heads, bucket,
-                                        self.impl.kv_cache_dtype)
-            self.kernel_launches_per_step = self.engine.num_layers * (2 + (1 if parts > 1 else 0))
+            _, parts, variant = ops.attn_plan(b, self.impl.num_heads, self.impl.num_kv_heads, bucket,
+                                              self.impl.kv_cache_dtype)
+            # fused step: one kernel per layer; otherwise append + attention (+ merge)
+            per_layer = 1 if variant == 2 else 2 + (1 if parts > 1 else 0)
+            self.kernel_launches_per_step = self.engine.num_layers * per_layer
             return  # the warm-up pass above already executed this step
         with torch.cuda.stream(self.stream):
             graph.replay()

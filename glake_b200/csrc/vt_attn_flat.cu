@@ -19,6 +19,11 @@
 // most two non-final pieces (its first and its last), hence two scratch slots
 // per CTA regardless of context length.
 //
+// Fused step: when the call carries this step's new K/V rows, the kernel is the
+// append as well.  The producer fetches the newest token's row from the input
+// tensors instead of the cache (so nothing depends on a prior append kernel), and
+// the consumer warp that holds that row in shared memory stores it to the range.
+//
 // Roofline: HBM.  Algorithmic bytes per (sequence, kv head): L * 2 * 128 * 2.
 #include "../../include/vtensor.h"
 #include "vt_device.cuh"
@@ -146,6 +151,11 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
       const int seq_len = p.seq_lens[pc.b];
       const char *base = reinterpret_cast<const char *>(lane < 16 ? p.k_table[slot] : p.v_table[slot]) +
                          static_cast<size_t>(pc.slab) * HS * kRowB;
+      const char *fresh = nullptr;   // this step's row of the slab, when the call is a fused step
+      if (p.new_key && p.byte_off[pc.b] >= 0)
+        fresh = (lane < 16 ? static_cast<const char *>(p.new_key) + pc.b * p.new_key_stride * 2
+                           : static_cast<const char *>(p.new_value) + pc.b * p.new_value_stride * 2) +
+                static_cast<size_t>(pc.slab) * HS * kRowB;
       for (int tile = pc.tile_begin; tile < pc.tile_end; ++tile, ++it) {
         const int s = it % kStages;
         if (it >= kStages && !mbar_wait(empty0 + 8 * s, ((it / kStages) - 1) & 1)) {
@@ -157,10 +167,18 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
         const int nt = min(TILE_TOK, seq_len - t0);
         if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2u * nt * HS * kRowB);
         __syncwarp();
-        const int rows = min(R, nt - grp * R);   // valid token rows of this lane's group
-        if (rows > 0)
-          bulk_g2s_hint(ring0 + s * kStageB + dst_lane, base + static_cast<size_t>(t0 + grp * R) * tok_pitch,
-                        rows * HS * kRowB, full0 + 8 * s, policy);
+        int rows = min(R, nt - grp * R);   // valid token rows of this lane's group
+        if (rows > 0) {
+          const uint32_t dst = ring0 + s * kStageB + dst_lane;
+          if (fresh && t0 + grp * R + rows == seq_len) {
+            // the newest token comes straight from this step's input row
+            --rows;
+            bulk_g2s(dst + rows * HS * kRowB, fresh, HS * kRowB, full0 + 8 * s);
+          }
+          if (rows > 0)
+            bulk_g2s_hint(dst, base + static_cast<size_t>(t0 + grp * R) * tok_pitch, rows * HS * kRowB,
+                          full0 + 8 * s, policy);
+        }
       }
       tau += pc.tile_end - pc.tile_begin;
     }
@@ -195,6 +213,14 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
     const Piece pc = locate(prefix, p.batch, slabs, tau, tau1);
     const int seq_len = p.seq_lens[pc.b];
     const int kv_head = pc.slab * HS + hs;
+    long long append_off = -1;
+    char *append_k = nullptr, *append_v = nullptr;
+    if (p.new_key) {
+      append_off = p.byte_off[pc.b];
+      const int64_t slot = p.slot_ids[pc.b];
+      append_k = reinterpret_cast<char *>(p.k_table[slot]);
+      append_v = reinterpret_cast<char *>(p.v_table[slot]);
+    }
     WarpAttn<NB> st;
     st.start(static_cast<const __nv_bfloat16 *>(p.q) + pc.b * p.q_stride + kv_head * g * kHeadDim, g, lane);
     for (int tile = pc.tile_begin; tile < pc.tile_end; ++tile, ++it) {
@@ -203,6 +229,15 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
       if (failed) continue;
       if (it == 0) VT_TR(2);
       const int tok0 = tile * TILE_TOK + rr;      // token of fragment row 0
+      if (append_off >= 0 && (seq_len - 1 - tok0) % R == 0 && seq_len - 1 >= tok0 &&
+          seq_len - 1 < (tile + 1) * TILE_TOK) {
+        // Fused step: this warp holds the newest token's row of its kv head; make it
+        // part of the cache (8 bytes per lane for K and for V).
+        const unsigned char *row = smem + s * kStageB + ((seq_len - 1 - tok0) / R) * kPitch + row_off;
+        const size_t dst = static_cast<size_t>(append_off) + static_cast<size_t>(kv_head) * kRowB + lane * 8;
+        *reinterpret_cast<uint2 *>(append_k + dst) = *reinterpret_cast<const uint2 *>(row + lane * 8);
+        *reinterpret_cast<uint2 *>(append_v + dst) = *reinterpret_cast<const uint2 *>(row + kTileB + lane * 8);
+      }
       if (tok0 < seq_len)
         st.tile(ring0 + s * kStageB, smem + s * kStageB, k_off, v_off, row_off,
                 min(16, (seq_len - tok0 + R - 1) / R), sl2, lane);

@@ -176,12 +176,13 @@ int vt_decode_attn_workspace_bytes(int batch, int h, int d, int max_seq_len, siz
   return VT_OK;
 }
 
-int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_stride,
+static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_t q_stride,
                    const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
                    const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len,
                    float scale, int kv_dtype, const float *k_scale, const float *v_scale,
                    float *lse, void *workspace, size_t workspace_bytes, int num_splits,
-                   void *stream) {
+                   void *stream, const void *new_key, const void *new_value, int64_t new_key_stride,
+                   int64_t new_value_stride, const int64_t *byte_off) {
   if (batch < 0 || h <= 0 || kvh <= 0 || max_seq_len < 0 || num_splits < 0) return VT_ERR_INVALID;
   if (batch == 0) return VT_OK;
   if (!out || !q || !k_table || !v_table || !slot_ids || !seq_lens || !workspace) return VT_ERR_INVALID;
@@ -202,7 +203,15 @@ int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_strid
   p.batch = batch; p.h = h; p.kvh = kvh; p.scale = scale; p.k_scale = k_scale; p.v_scale = v_scale;
   p.lse = lse; p.part_tokens = plan.part_tokens; p.max_parts = plan.max_parts;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (new_key && plan.variant != 2) {
+    // no fused kernel for this shape / dtype: append first, then attend
+    int st = vt_append(new_key, new_value, new_key_stride, new_value_stride, k_table, v_table, byte_off, slot_ids,
+                       nullptr, nullptr, 1, batch, kvh, d, kv_dtype, k_scale, v_scale, stream);
+    if (st != VT_OK) return st;
+  }
   if (plan.variant == 2) {
+    p.new_key = new_key; p.new_value = new_value;
+    p.new_key_stride = new_key_stride; p.new_value_stride = new_value_stride; p.byte_off = byte_off;
     vt::carve_flat(workspace, batch, kvh, &p);
     p.n_ctas = vt::flat_grid();
 #ifdef VT_TRACE
@@ -273,6 +282,35 @@ int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype
   if (max_parts) *max_parts = plan.max_parts;
   if (variant) *variant = plan.variant;
   return VT_OK;
+}
+
+int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_stride,
+                   const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
+                   const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len,
+                   float scale, int kv_dtype, const float *k_scale, const float *v_scale,
+                   float *lse, void *workspace, size_t workspace_bytes, int num_splits,
+                   void *stream) {
+  return decode_attn_impl(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, batch, h, kvh, d,
+                          max_seq_len, scale, kv_dtype, k_scale, v_scale, lse, workspace, workspace_bytes, num_splits,
+                          stream, nullptr, nullptr, 0, 0, nullptr);
+}
+
+int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *key,
+                   const void *value, int64_t key_stride, int64_t value_stride, const int64_t *byte_off,
+                   const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
+                   const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len, float scale,
+                   int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
+                   size_t workspace_bytes, void *stream) {
+  if (batch < 0 || kvh <= 0) return VT_ERR_INVALID;
+  if (batch == 0) return VT_OK;
+  if (!key || !value || !byte_off) return VT_ERR_INVALID;
+  if ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 15) return VT_ERR_INVALID;
+  if ((key_stride % 8) || (value_stride % 8) || key_stride < static_cast<int64_t>(kvh) * d ||
+      value_stride < static_cast<int64_t>(kvh) * d)
+    return VT_ERR_INVALID;
+  return decode_attn_impl(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, batch, h, kvh, d,
+                          max_seq_len, scale, kv_dtype, k_scale, v_scale, lse, workspace, workspace_bytes, 0, stream,
+                          key, value, key_stride, value_stride, byte_off);
 }
 
 int vt_decode_attn_status(void *workspace, void *stream, int *code) {

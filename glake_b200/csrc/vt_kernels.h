@@ -37,6 +37,10 @@ struct AttnParams {
   int n_ctas;                         // grid size
   unsigned *fl_count;                 // [batch * kv-head slabs] piece tickets, zero between launches
   float *fl_part;                     // [n_ctas, 2 slots, 4 warps, 8 or 16 heads, 132] piece states
+  // fused step (flat schedule only): this step's K/V rows, appended by the attention kernel itself
+  const void *new_key, *new_value;    // bf16 [batch, kvh, 128]; nullptr = plain attention
+  int64_t new_key_stride, new_value_stride;   // elements per batch row
+  const int64_t *byte_off;            // destination byte offset per entry (negative = nothing to append)
 #ifdef VT_TRACE
   unsigned long long *trace;          // debug builds only: per-CTA timestamps
 #endif

@@ -13,38 +13,45 @@ import sys
 import torch
 from . import ops, vmmAllocator as A
 from .backend import VTensorCacheEngine, VTensorMetadata, prepare_step
-B,H,KVH,LO,HI = map(int, sys.argv[1:6])
-fp8 = len(sys.argv)>6 and sys.argv[6]=='1'
-splits = int(sys.argv[7]) if len(sys.argv)>7 else 0
-iters = int(sys.argv[8]) if len(sys.argv)>8 else 20
-e = 1 if fp8 else 2
-g = torch.Generator().manual_seed(0)
-lens = torch.randint(LO, HI+1, (B,), generator=g).tolist()
-row = KVH*128*e
-need = sum((n*row + (2<<20)-1)//(2<<20) for n in lens)*2 + 16
-torch.cuda.set_device(0); torch.zeros(1,device='cuda')
-assert A.init_physical_handle(need, 0)
-dt = 'fp8_e4m3' if fp8 else 'auto'
-eng = VTensorCacheEngine(1, KVH, 128, B, HI+8, cache_dtype=dt)
-meta = VTensorMetadata(list(range(B)), lens, KVH, 128, num_prefills=B, kv_elem_size=e)
-prepare_step(meta, eng)
-tot = sum(lens)
-ks = torch.full((KVH,), 5/448, device='cuda'); vs = ks.clone()
-kcat = torch.randn(tot, KVH, 128, device='cuda', dtype=torch.bfloat16); vcat = torch.randn(tot, KVH, 128, device='cuda', dtype=torch.bfloat16)
-ops.reshape_and_cache(kcat, vcat, eng.k_cache_ptr[0], eng.v_cache_ptr[0], meta.slot_m, meta.slot_mapping, meta.seq_lens_tensor, meta.cache_seq_lens, max(lens), KVH, 128, dt, ks if fp8 else None, vs if fp8 else None)
-del kcat, vcat
-q = torch.randn(B,H,128, device='cuda', dtype=torch.bfloat16); out = torch.empty_like(q)
-kc, vc = eng.gpu_cache[0]
-def run():
-    ops.paged_attention_v1(out, q, kc.vmm_ptr, vc.vmm_ptr, KVH, 128**-0.5, meta.seq_lens_tensor, 1, max(lens), None, dt, 1.0, meta.slot_mapping, k_scale=ks if fp8 else None, v_scale=vs if fp8 else None, num_splits=splits)
-for _ in range(3): run()
-torch.cuda.synchronize()
-flush = torch.zeros(64<<20, dtype=torch.float32, device='cuda')
-ts=[]
-for _ in range(iters):
-    flush.sum()  # read-only L2 flush: leaves clean lines behind
-    a,z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    a.record(); run(); z.record(); torch.cuda.synchronize(); ts.append(a.elapsed_time(z))
-ts.sort(); ms = ts[len(ts)//2]
-byt = tot*2*KVH*128*e + 2*B*H*128*2
-print(f"B{B} H{H} KVH{KVH} L[{LO},{HI}] fp8={fp8} splits={splits} plan={ops.attn_plan(B,H,KVH,max(lens),dt,splits)}: {ms*1e3:.1f} us  {byt/ms/1e6:.0f} GB/s  ({byt/2**20:.0f} MiB) min {byt/ts[0]/1e6:.0f}", flush=True)
+
+
+def main():
+    B,H,KVH,LO,HI = map(int, sys.argv[1:6])
+    fp8 = len(sys.argv)>6 and sys.argv[6]=='1'
+    splits = int(sys.argv[7]) if len(sys.argv)>7 else 0
+    iters = int(sys.argv[8]) if len(sys.argv)>8 else 20
+    e = 1 if fp8 else 2
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(LO, HI+1, (B,), generator=g).tolist()
+    row = KVH*128*e
+    need = sum((n*row + (2<<20)-1)//(2<<20) for n in lens)*2 + 16
+    torch.cuda.set_device(0); torch.zeros(1,device='cuda')
+    assert A.init_physical_handle(need, 0)
+    dt = 'fp8_e4m3' if fp8 else 'auto'
+    eng = VTensorCacheEngine(1, KVH, 128, B, HI+8, cache_dtype=dt)
+    meta = VTensorMetadata(list(range(B)), lens, KVH, 128, num_prefills=B, kv_elem_size=e)
+    prepare_step(meta, eng)
+    tot = sum(lens)
+    ks = torch.full((KVH,), 5/448, device='cuda'); vs = ks.clone()
+    kcat = torch.randn(tot, KVH, 128, device='cuda', dtype=torch.bfloat16); vcat = torch.randn(tot, KVH, 128, device='cuda', dtype=torch.bfloat16)
+    ops.reshape_and_cache(kcat, vcat, eng.k_cache_ptr[0], eng.v_cache_ptr[0], meta.slot_m, meta.slot_mapping, meta.seq_lens_tensor, meta.cache_seq_lens, max(lens), KVH, 128, dt, ks if fp8 else None, vs if fp8 else None)
+    del kcat, vcat
+    q = torch.randn(B,H,128, device='cuda', dtype=torch.bfloat16); out = torch.empty_like(q)
+    kc, vc = eng.gpu_cache[0]
+    def run():
+        ops.paged_attention_v1(out, q, kc.vmm_ptr, vc.vmm_ptr, KVH, 128**-0.5, meta.seq_lens_tensor, 1, max(lens), None, dt, 1.0, meta.slot_mapping, k_scale=ks if fp8 else None, v_scale=vs if fp8 else None, num_splits=splits)
+    for _ in range(3): run()
+    torch.cuda.synchronize()
+    flush = torch.zeros(64<<20, dtype=torch.float32, device='cuda')
+    ts=[]
+    for _ in range(iters):
+        flush.sum()  # read-only L2 flush: leaves clean lines behind
+        a,z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(); run(); z.record(); torch.cuda.synchronize(); ts.append(a.elapsed_time(z))
+    ts.sort(); ms = ts[len(ts)//2]
+    byt = tot*2*KVH*128*e + 2*B*H*128*2
+    print(f"B{B} H{H} KVH{KVH} L[{LO},{HI}] fp8={fp8} splits={splits} plan={ops.attn_plan(B,H,KVH,max(lens),dt,splits)}: {ms*1e3:.1f} us  {byt/ms/1e6:.0f} GB/s  ({byt/2**20:.0f} MiB) min {byt/ts[0]/1e6:.0f}", flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -148,6 +148,27 @@ def fwd_kvcache(q, k_table_ptr, v_table_ptr, max_seq_len, num_kv_heads, batch, s
     return o, lse.unsqueeze(-1)
 
 
+def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_mapping, seq_lens, max_seq_len,
+                num_kv_heads, scale, kv_cache_dtype="auto", k_scale=None, v_scale=None, lse=None):
+    """``reshape_and_cache`` (decode form) + ``paged_attention_v1`` in one call; one
+    kernel launch for a bf16 cache.  ``key_cache`` / ``value_cache`` are the device
+    addresses of the layer's pointer tables (ints), ``slot_m`` the destination byte
+    offsets, ``slot_mapping`` the slot ids, ``seq_lens`` the contexts INCLUDING the
+    appended token.  query/out ``[B, H, D]``, key/value ``[B, KVH, D]`` bf16."""
+    _require_cuda(out, query, key, value, slot_m, slot_mapping, seq_lens)
+    batch, num_heads, head_size = query.shape
+    key = key.view(batch, num_kv_heads, head_size)
+    value = value.view(batch, num_kv_heads, head_size)
+    ws = attn_workspace(query.device, batch, num_heads, head_size, max_seq_len)
+    with torch.cuda.device(query.device):
+        check(lib.vt_decode_step(_ptr(out), out.stride(0), _ptr(query), query.stride(0), _ptr(key), _ptr(value),
+                                 key.stride(0), value.stride(0), _ptr(slot_m), c_void_p(int(key_cache)),
+                                 c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens), batch, num_heads,
+                                 num_kv_heads, head_size, int(max_seq_len), float(scale), _kv_dtype(kv_cache_dtype),
+                                 _ptr(k_scale), _ptr(v_scale), _ptr(lse), _ptr(ws), ws.numel(), _stream()),
+              "vt_decode_step")
+
+
 def attn_plan(batch, num_heads, num_kv_heads, max_seq_len, kv_cache_dtype="auto", num_splits=0):
     """(tokens per partition, partitions per sequence, kernel variant) the library
     picks for this problem size."""

@@ -230,6 +230,24 @@ int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_strid
 int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits,
                         int *part_tokens, int *max_parts, int *variant);
 
+/* One decode step of a layer in a single call: append this step's K/V rows
+ * (vt_append with max_seq_len == 1) and attend (vt_decode_attn).  Results are
+ * identical to the two calls in sequence; seq_lens INCLUDES the appended token and
+ * byte_off[i] is its destination offset, as extend_kv_cache_batch returned it.
+ * With bf16 KV the two are ONE kernel launch: the attention kernel reads the
+ * newest row from key / value directly and stores it into the range itself, so
+ * the step has no append launch and no dependency between the two.  Otherwise the
+ * call enqueues the append kernel followed by the attention kernels.
+ * Replaces the pair of calls in XFormersImpl.forward
+ * (vllm/attention/backends/xformers.py:310-312 and :407-430).
+ * key / value must be 16-byte aligned with strides that are multiples of 8 elements. */
+int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *key,
+                   const void *value, int64_t key_stride, int64_t value_stride, const int64_t *byte_off,
+                   const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
+                   const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len, float scale,
+                   int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
+                   size_t workspace_bytes, void *stream);
+
 /* vt_decode_attn for callers that cannot allocate device memory at all.
  * (No counterpart in the reference: its attention ops get their scratch from
  * torch's allocator.)

@@ -188,6 +188,61 @@ def test_fp8_kv_cache(G, oracle, h, kvh):
         kv16.close()
 
 
+@pytest.mark.parametrize("h,kvh,fp8", [(8, 1, False), (8, 2, False), (8, 4, False), (32, 32, False), (16, 1, False),
+                                        (3, 3, False), (8, 8, True)])
+def test_fused_decode_step_appends_and_attends(G, oracle, h, kvh, fp8):
+    """vt_decode_step = append + attention in one call (one launch for bf16): the
+    cache must hold the new rows bit for bit afterwards and the output must match
+    the oracle on the extended context, over several steps incl. tile and chunk
+    boundaries (63/64/65 tokens, 2 MiB crossing for 8 KiB rows)."""
+    from glake_b200 import ops
+    from glake_b200.backend import VTensorMetadata, prepare_step
+    lens = [1, 62, 63, 64, 255, 700]
+    rs = np.random.RandomState(321 + h)
+    q0, k, v = synth.make_case(50 + h + kvh, lens, h, kvh)
+    ks = vs = None
+    if fp8:
+        ks = ops.kv_scales(torch.cat(k).cuda(), kvh, 128)
+        vs = ops.kv_scales(torch.cat(v).cuda(), kvh, 128)
+    kv = G.GpuKV(k, v, kvh, fp8=fp8, k_scale=ks, v_scale=vs)
+    try:
+        dt = "fp8_e4m3" if fp8 else "auto"
+        for step in range(3):
+            nk = synth.normal_bf16(rs, len(lens), kvh, 128)
+            nv = synth.normal_bf16(rs, len(lens), kvh, 128)
+            q = synth.normal_bf16(rs, len(lens), h, 128)
+            lens = [n + 1 for n in lens]
+            k = [torch.cat([a, b[None]]) for a, b in zip(k, nk)]
+            v = [torch.cat([a, b[None]]) for a, b in zip(v, nv)]
+            meta = VTensorMetadata(kv.slots, lens, kvh, 128, num_decode_tokens=len(lens), kv_elem_size=1 if fp8 else 2)
+            prepare_step(meta, kv.engine)
+            out = torch.empty(len(lens), h, 128, dtype=torch.bfloat16, device="cuda")
+            ops.decode_step(out, q.cuda(), nk.cuda(), nv.cuda(), kv.k_table, kv.v_table, meta.slot_m, meta.slot_mapping,
+                            meta.seq_lens_tensor, meta.max_seq_len, kvh, SCALE, dt, ks, vs)
+            torch.cuda.synchronize()
+            kv.lens = lens
+            if fp8:
+                r = oracle.fill_ranges(k, v, k_scale=ks.cpu(), v_scale=vs.cpu())
+                for i, n in enumerate(lens):
+                    assert torch.equal(kv.read_rows(i, "k"), r.k_rows(i, n, kvh, 128, fp8=True))
+                port = oracle.port_decode_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32),
+                                               kvh, SCALE, ks.cpu(), vs.cpu())
+                # the reference's own fp8 tolerance, or two bf16 ulps where the short
+                # contexts make outputs O(1) (the oracle rounds dequantised values to bf16)
+                err = (out.cpu().float() - port.float()).abs()
+                assert bool((err <= torch.maximum(torch.full_like(err, 1e-2), port.float().abs() * 2.0 ** -6)).all())
+            else:
+                for i in range(len(lens)):
+                    assert torch.equal(kv.read_rows(i, "k"), k[i]) and torch.equal(kv.read_rows(i, "v"), v[i])
+                r = oracle.fill_ranges(k, v)
+                port = oracle.port_decode_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32),
+                                               kvh, SCALE)
+                ok, err = close_2e3(out.cpu(), port, ulp_slack=True)
+                assert ok, (step, err)
+    finally:
+        kv.close()
+
+
 def test_backend_forward_decode_steps(G, oracle):
     """The attention-backend binding over several decode steps and two layers:
     prepare_step -> reshape_and_cache -> fwd_kvcache, against the oracle."""
