@@ -50,8 +50,12 @@ constexpr int kThreads = kMmaThreads;
 constexpr int kRing = kStages * kStageB;
 constexpr int kPartRow = kFlatPartRow;   // floats per published (q head, warp) state: O[128], max, sum, pad
 
+constexpr int kBaseCacheMaxBatch = 256;   // per-sequence base addresses are cached in shared memory up to here
+
+// ring | barriers | flags | prefix[batch + 1] | lens[batch] | (pad to 8) | kbase[batch] | vbase[batch]
+__host__ __device__ constexpr int flat_meta_ints(int batch) { return ((2 * batch + 1 + 4) + 1) / 2 * 2; }
 __host__ __device__ constexpr int flat_smem_bytes(int batch) {
-  return kRing + 2 * kStages * 8 + 16 + (batch + 1) * 4;
+  return kRing + 2 * kStages * 8 + flat_meta_ints(batch) * 4 + (batch <= kBaseCacheMaxBatch ? batch * 16 : 0);
 }
 
 struct Piece {
@@ -94,6 +98,10 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kRing);
   int *flags = reinterpret_cast<int *>(smem + kRing + 2 * kStages * 8);   // [0] = "this CTA merges"
   int *prefix = flags + 4;                                                // [batch + 1]
+  int *lens = prefix + p.batch + 1;                                       // [batch] context lengths
+  const bool cache_bases = p.batch <= kBaseCacheMaxBatch;
+  unsigned long long *kbase_s = reinterpret_cast<unsigned long long *>(flags + flat_meta_ints(p.batch));
+  unsigned long long *vbase_s = kbase_s + p.batch;                        // [batch] each, only if cache_bases
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
   const uint32_t ring0 = smem_u32(smem);
 
@@ -109,8 +117,16 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
     mbar_fence_init();
   }
   // tiles per sequence, then an exclusive prefix (batch is small: one warp scans it)
-  for (int i = threadIdx.x; i < p.batch; i += kThreads)
-    prefix[i + 1] = ((max(p.seq_lens[i], 0) + TILE_TOK - 1) / TILE_TOK) * slabs;
+  for (int i = threadIdx.x; i < p.batch; i += kThreads) {
+    const int len = max(p.seq_lens[i], 0);
+    lens[i] = len;
+    prefix[i + 1] = ((len + TILE_TOK - 1) / TILE_TOK) * slabs;
+    if (cache_bases) {   // resolve slot -> range base once, off the producer's critical path
+      const int64_t slot = p.slot_ids[i];
+      kbase_s[i] = p.k_table[slot];
+      vbase_s[i] = p.v_table[slot];
+    }
+  }
   __syncthreads();
   if (warp == 0) {
     int carry = 0;
@@ -147,10 +163,15 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
     int it = 0;  // tiles issued by this CTA: ring position and barrier phase
     for (long long tau = tau0; tau < tau1;) {
       const Piece pc = locate(prefix, p.batch, slabs, tau, tau1);
-      const int64_t slot = p.slot_ids[pc.b];
-      const int seq_len = p.seq_lens[pc.b];
-      const char *base = reinterpret_cast<const char *>(lane < 16 ? p.k_table[slot] : p.v_table[slot]) +
-                         static_cast<size_t>(pc.slab) * HS * kRowB;
+      const int seq_len = lens[pc.b];
+      unsigned long long range;
+      if (cache_bases) {
+        range = lane < 16 ? kbase_s[pc.b] : vbase_s[pc.b];
+      } else {
+        const int64_t slot = p.slot_ids[pc.b];
+        range = lane < 16 ? p.k_table[slot] : p.v_table[slot];
+      }
+      const char *base = reinterpret_cast<const char *>(range) + static_cast<size_t>(pc.slab) * HS * kRowB;
       const char *fresh = nullptr;   // this step's row of the slab, when the call is a fused step
       if (p.new_key && p.byte_off[pc.b] >= 0)
         fresh = (lane < 16 ? static_cast<const char *>(p.new_key) + pc.b * p.new_key_stride * 2
@@ -211,15 +232,20 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
   bool first_piece = true;
   for (long long tau = tau0; tau < tau1;) {
     const Piece pc = locate(prefix, p.batch, slabs, tau, tau1);
-    const int seq_len = p.seq_lens[pc.b];
+    const int seq_len = lens[pc.b];
     const int kv_head = pc.slab * HS + hs;
     long long append_off = -1;
     char *append_k = nullptr, *append_v = nullptr;
     if (p.new_key) {
       append_off = p.byte_off[pc.b];
-      const int64_t slot = p.slot_ids[pc.b];
-      append_k = reinterpret_cast<char *>(p.k_table[slot]);
-      append_v = reinterpret_cast<char *>(p.v_table[slot]);
+      if (cache_bases) {
+        append_k = reinterpret_cast<char *>(kbase_s[pc.b]);
+        append_v = reinterpret_cast<char *>(vbase_s[pc.b]);
+      } else {
+        const int64_t slot = p.slot_ids[pc.b];
+        append_k = reinterpret_cast<char *>(p.k_table[slot]);
+        append_v = reinterpret_cast<char *>(p.v_table[slot]);
+      }
     }
     WarpAttn<NB> st;
     st.start(static_cast<const __nv_bfloat16 *>(p.q) + pc.b * p.q_stride + kv_head * g * kHeadDim, g, lane);
@@ -273,8 +299,36 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
     } else {
       // Publish this piece, draw a ticket, and merge the stream if it was the last one.
       const int slot_id = first_piece ? 0 : 1;
-      st.template store<kPartRow>(
-          p.fl_part + ((static_cast<size_t>(blockIdx.x) * 2 + slot_id) * kCWarps + warp) * HEADS * kPartRow, lane, g);
+      float *slot_base = p.fl_part + (static_cast<size_t>(blockIdx.x) * 2 + slot_id) * kCWarps * HEADS * kPartRow;
+      const bool last_of_cta = tau + (pc.tile_end - pc.tile_begin) == tau1;
+      if (R > 1 && last_of_cta) {
+        // The ring is idle after the CTA's last tile: fold the R warps of every kv
+        // head together in shared memory first, so the piece publishes one state
+        // per head instead of R (fewer bytes out, fewer sources for the merger).
+        named_bar_sync(1, kCWarps * 32);                       // all warps are done with the ring
+        float *mbuf = reinterpret_cast<float *>(smem);          // [kCWarps][HEADS][kPartRow]
+        st.template store<kPartRow>(mbuf + warp * HEADS * kPartRow, lane, g);
+        named_bar_sync(1, kCWarps * 32);
+        for (int hh = 0; hh < HS; ++hh)
+          for (int head = 0; head < g; ++head) {
+            float M = -INFINITY;
+#pragma unroll
+            for (int r = 0; r < R; ++r) M = fmaxf(M, mbuf[((r * HS + hh) * HEADS + head) * kPartRow + 128]);
+            float L = 0.f, O = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              const float *src = mbuf + ((r * HS + hh) * HEADS + head) * kPartRow;
+              const float f = exp2f(src[128] - M);   // M is finite: row 0 of the piece's first tile is valid
+              L = fmaf(f, src[129], L);
+              O = fmaf(f, src[tid], O);
+            }
+            float *dst = slot_base + (hh * HEADS + head) * kPartRow;
+            dst[tid] = O;
+            if (tid == 0) { dst[128] = M; dst[129] = L; }
+          }
+      } else {
+        st.template store<kPartRow>(slot_base + warp * HEADS * kPartRow, lane, g);
+      }
       __threadfence();
       named_bar_sync(1, kCWarps * 32);
       const long long s_begin = pc.stream_begin, s_end = pc.stream_begin + pc.tiles_in_stream;
@@ -297,7 +351,11 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
         // (max, sum) of source i, the warp agrees on the stream maximum, then every
         // lane accumulates its 4 output dims over the sources with independent
         // 16-byte loads.  Streams cut into more than 32 sources go in rounds.
-        const int n_src = n_pieces * R;
+        // Pieces that were their CTA's last piece arrive folded (one row per head):
+        // that is every piece but, possibly, the one in the stream's last CTA.
+        const bool last_folded = R == 1 || s_end >= total * (c_last + 1) / n_ctas;
+        const int n_single = last_folded ? n_pieces : n_pieces - 1;
+        const int n_src = R == 1 ? n_pieces : n_single + (last_folded ? 0 : R);
         for (int item = warp; item < HS * g; item += kCWarps) {
           const int hh = item / g, head = item % g;
           float M = -INFINITY, L = 0.f;
@@ -307,7 +365,8 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
             const float *mine = nullptr;
             float mi = -INFINITY, li = 0.f;
             if (i < n_src) {
-              const int c = c_first + i / R, r = i % R;
+              const int c = i < n_single ? c_first + i : c_last;
+              const int r = i < n_single ? 0 : i - n_single;
               // the stream is CTA c's first piece iff it already runs at c's first tile
               const int sl = (s_begin <= total * c / n_ctas) ? 0 : 1;
               mine = p.fl_part + (((static_cast<size_t>(c) * 2 + sl) * kCWarps + r * HS + hh) * HEADS + head) * kPartRow;

@@ -46,7 +46,7 @@ struct AttnParams {
 #endif
 };
 
-constexpr int kFlatMaxBatch = 2048;   // prefix table of the flat schedule lives in shared memory
+constexpr int kFlatMaxBatch = 1024;   // prefix table of the flat schedule lives in shared memory
 constexpr int kFlatPartRow = 132;     // floats per published piece state row (16-byte aligned)
 constexpr int kFlatMaxCtas = 320;     // 2 per SM on up to 160 SMs
 
