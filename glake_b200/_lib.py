@@ -15,6 +15,7 @@ VT_ERR_INVALID, VT_ERR_DRIVER, VT_ERR_POOL_EMPTY, VT_ERR_RESERVE, VT_ERR_TIMEOUT
 VT_ERR_UNSUPPORTED, VT_ERR_CUDA, VT_ERR_STATE, VT_ERR_NO_DRIVER, VT_ERR_KERNEL = 6, 7, 8, 9, 10
 VT_ERR_TOO_LARGE = 11
 VT_STATIC_SCRATCH_BYTES = 12 << 20
+VT_STEP_OVERLAP = 1
 VT_KV_BF16, VT_KV_FP8_E4M3 = 0, 1
 
 
@@ -79,7 +80,7 @@ def _load():
         "vt_decode_attn": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                                    c_float, c_int, vp, vp, vp, vp, sz, c_int, vp]),
         "vt_decode_step": (c_int, [vp, c_int64, vp, c_int64, vp, vp, c_int64, c_int64, vp, vp, vp, vp, vp, c_int, c_int,
-                                   c_int, c_int, c_int, c_float, c_int, vp, vp, vp, vp, sz, vp]),
+                                   c_int, c_int, c_int, c_float, c_int, vp, vp, vp, vp, sz, ctypes.c_uint, vp]),
         "vt_decode_attn_static": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                                           c_float, c_int, vp, vp, vp, c_int, vp]),
         "vt_decode_attn_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int),

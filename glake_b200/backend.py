@@ -189,8 +189,10 @@ class DecodeRunner:
     BUCKET = 2048  # graphs are keyed by max context rounded up to this many tokens
 
     def __init__(self, engine: VTensorCacheEngine, impl: VTensorAttentionImpl, batch, host_io=False,
-                 k_scale=None, v_scale=None):
+                 k_scale=None, v_scale=None, overlap=True):
         self.engine, self.impl, self.batch, self.host_io = engine, impl, batch, host_io
+        # consecutive layers touch disjoint ranges: let layer l+1 start as layer l drains
+        self.overlap = overlap and engine.num_layers > 1
         self.k_scale, self.v_scale = k_scale, v_scale
         dev, layers = engine.device, engine.num_layers
         hd, kd = impl.num_heads * impl.head_size, impl.num_kv_heads * impl.head_size
@@ -206,6 +208,7 @@ class DecodeRunner:
             self.hq, self.hk, self.hv = (torch.zeros_like(t, device="cpu").pin_memory() for t in (self.q, self.k, self.v))
             self.hout = torch.zeros_like(self.out, device="cpu").pin_memory()
         self.graphs = {}
+        self.workspace = None   # private scratch: the overlapped launches need it zero-filled and to themselves
         self.kernel_launches_per_step = 0
         self.stream = torch.cuda.Stream(device=dev)
 
@@ -226,7 +229,7 @@ class DecodeRunner:
                             self.q[layer].view(b, self.impl.num_heads, self.impl.head_size), self.k[layer],
                             self.v[layer], kc.vmm_ptr, vc.vmm_ptr, self.d64[:b], self.d64[b:], self.d32[:b],
                             meta.max_seq_len, self.impl.num_kv_heads, self.impl.scale, self.impl.kv_cache_dtype,
-                            ks, vs)
+                            ks, vs, overlap=self.overlap and layer > 0, workspace=self.workspace)
         if self.host_io:
             self.hout.copy_(self.out, non_blocking=True)
 
@@ -246,6 +249,11 @@ class DecodeRunner:
         bucket = (meta.max_seq_len + self.BUCKET - 1) // self.BUCKET * self.BUCKET
         graph = self.graphs.get(bucket)
         if graph is None:
+            need = ops.new_workspace(self.engine.device, b, self.impl.num_heads, self.impl.head_size, bucket)
+            if self.workspace is None or self.workspace.numel() < need.numel():
+                self.stream.synchronize()
+                self.workspace = need
+                self.graphs.clear()     # older graphs captured the previous buffer's address
             capture_meta = VTensorMetadata(meta.slot_mapping_list, meta.seq_lens, meta.kv_num_heads,
                                            meta.kv_head_size, kv_elem_size=meta.kv_elem_size)
             capture_meta.max_seq_len = bucket

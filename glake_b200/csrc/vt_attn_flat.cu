@@ -24,6 +24,13 @@
 // tensors instead of the cache (so nothing depends on a prior append kernel), and
 // the consumer warp that holds that row in shared memory stores it to the range.
 //
+// Overlap with the previous step (opt-in): consecutive layers' launches touch
+// disjoint ranges, so with programmatic dependent launch a CTA of the next layer
+// may take an SM slot as soon as a CTA of this layer exits, and stream its K/V
+// while this layer's stragglers and mergers finish.  The only thing the two grids
+// share is the scratch buffer; a dependent grid executes griddepcontrol.wait
+// before its first access to it.
+//
 // Roofline: HBM.  Algorithmic bytes per (sequence, kv head): L * 2 * 128 * 2.
 #include "../../include/vtensor.h"
 #include "vt_device.cuh"
@@ -145,6 +152,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
   }
   __syncthreads();
   VT_TR(1);
+  pdl_launch_dependents();   // the next launch may be scheduled as CTAs of this grid exit
   const long long total = prefix[p.batch];
   // Only min(grid, total) CTAs take part, so that every participating CTA owns at
   // least one tile and the piece count of a stream is a plain difference.
@@ -298,6 +306,9 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
       }
     } else {
       // Publish this piece, draw a ticket, and merge the stream if it was the last one.
+      // The scratch is shared with the previous launch: a dependent grid must see
+      // that one finished (mergers done reading, counters back to zero) first.
+      if (p.overlap) pdl_wait_prior_grid();
       const int slot_id = first_piece ? 0 : 1;
       float *slot_base = p.fl_part + (static_cast<size_t>(blockIdx.x) * 2 + slot_id) * kCWarps * HEADS * kPartRow;
       const bool last_of_cta = tau + (pc.tile_end - pc.tile_begin) == tau1;
@@ -436,6 +447,19 @@ int launch(const AttnParams &p, cudaStream_t stream) {
         cudaSuccess)
       return VT_ERR_CUDA;
     configured = smem;
+  }
+  if (p.overlap) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(p.n_ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, attn_flat_kernel<NB, HS, R>, p) == cudaSuccess ? VT_OK : VT_ERR_CUDA;
   }
   attn_flat_kernel<NB, HS, R><<<p.n_ctas, kThreads, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;

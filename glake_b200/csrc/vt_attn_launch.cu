@@ -182,7 +182,7 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
                    float scale, int kv_dtype, const float *k_scale, const float *v_scale,
                    float *lse, void *workspace, size_t workspace_bytes, int num_splits,
                    void *stream, const void *new_key, const void *new_value, int64_t new_key_stride,
-                   int64_t new_value_stride, const int64_t *byte_off) {
+                   int64_t new_value_stride, const int64_t *byte_off, unsigned flags) {
   if (batch < 0 || h <= 0 || kvh <= 0 || max_seq_len < 0 || num_splits < 0) return VT_ERR_INVALID;
   if (batch == 0) return VT_OK;
   if (!out || !q || !k_table || !v_table || !slot_ids || !seq_lens || !workspace) return VT_ERR_INVALID;
@@ -217,7 +217,13 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
 #ifdef VT_TRACE
     p.trace = getenv("VT_TRACE_PTR") ? reinterpret_cast<unsigned long long *>(strtoull(getenv("VT_TRACE_PTR"), nullptr, 0)) : nullptr;
 #endif
-    if (cudaMemsetAsync(p.fl_count, 0, static_cast<size_t>(batch) * kvh * sizeof(unsigned), s) != cudaSuccess)
+    p.overlap = (flags & VT_STEP_OVERLAP) ? 1 : 0;
+    // The ticket counters return to zero at the end of every launch.  They are
+    // cleared here anyway so that a scratch buffer of unknown content works — except
+    // in overlap mode, where a memset between the kernels would serialise them and
+    // the caller guarantees a zero-initialised buffer instead.
+    if (!p.overlap &&
+        cudaMemsetAsync(p.fl_count, 0, static_cast<size_t>(batch) * kvh * sizeof(unsigned), s) != cudaSuccess)
       return VT_ERR_CUDA;
     return vt::launch_attn_flat(p, kv_dtype, s);
   }
@@ -292,7 +298,7 @@ int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_strid
                    void *stream) {
   return decode_attn_impl(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, batch, h, kvh, d,
                           max_seq_len, scale, kv_dtype, k_scale, v_scale, lse, workspace, workspace_bytes, num_splits,
-                          stream, nullptr, nullptr, 0, 0, nullptr);
+                          stream, nullptr, nullptr, 0, 0, nullptr, 0u);
 }
 
 int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *key,
@@ -300,8 +306,8 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
                    const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
                    const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len, float scale,
                    int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
-                   size_t workspace_bytes, void *stream) {
-  if (batch < 0 || kvh <= 0) return VT_ERR_INVALID;
+                   size_t workspace_bytes, unsigned flags, void *stream) {
+  if (batch < 0 || kvh <= 0 || (flags & ~static_cast<unsigned>(VT_STEP_OVERLAP))) return VT_ERR_INVALID;
   if (batch == 0) return VT_OK;
   if (!key || !value || !byte_off) return VT_ERR_INVALID;
   if ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 15) return VT_ERR_INVALID;
@@ -310,7 +316,7 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
     return VT_ERR_INVALID;
   return decode_attn_impl(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, batch, h, kvh, d,
                           max_seq_len, scale, kv_dtype, k_scale, v_scale, lse, workspace, workspace_bytes, 0, stream,
-                          key, value, key_stride, value_stride, byte_off);
+                          key, value, key_stride, value_stride, byte_off, flags);
 }
 
 int vt_decode_attn_status(void *workspace, void *stream, int *code) {

@@ -70,6 +70,13 @@ __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   return p;
 }
 
+// Programmatic dependent launch (sm_90+): let the next kernel on the stream start
+// once every CTA of this grid has passed this point (or exited) ...
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// ... and, in that next kernel, wait until the previous grid has completed and its
+// writes are visible.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_wait_prior_grid() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }

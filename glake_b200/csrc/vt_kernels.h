@@ -41,6 +41,7 @@ struct AttnParams {
   const void *new_key, *new_value;    // bf16 [batch, kvh, 128]; nullptr = plain attention
   int64_t new_key_stride, new_value_stride;   // elements per batch row
   const int64_t *byte_off;            // destination byte offset per entry (negative = nothing to append)
+  int overlap;                        // launched as a programmatic dependent of the previous kernel on the stream
 #ifdef VT_TRACE
   unsigned long long *trace;          // debug builds only: per-CTA timestamps
 #endif

@@ -37,6 +37,14 @@ def _kv_dtype(kv_cache_dtype):
     raise RuntimeError(f"unsupported kv_cache_dtype {kv_cache_dtype!r} (bf16 and fp8_e4m3 only)")
 
 
+def new_workspace(device, batch, num_heads, head_size, max_seq_len):
+    """A private, zero-filled scratch buffer for ``decode_step(..., workspace=...)``."""
+    need = c_size_t()
+    check(lib.vt_decode_attn_workspace_bytes(batch, num_heads, head_size, max_seq_len, byref(need)),
+          "vt_decode_attn_workspace_bytes")
+    return torch.zeros(need.value, dtype=torch.uint8, device=device)
+
+
 def attn_workspace(device, batch, num_heads, head_size, max_seq_len):
     """Scratch for the split-K partials, cached per device and grown on demand.
     One buffer serves every layer because layers run back to back on one stream."""
@@ -149,23 +157,31 @@ def fwd_kvcache(q, k_table_ptr, v_table_ptr, max_seq_len, num_kv_heads, batch, s
 
 
 def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_mapping, seq_lens, max_seq_len,
-                num_kv_heads, scale, kv_cache_dtype="auto", k_scale=None, v_scale=None, lse=None):
+                num_kv_heads, scale, kv_cache_dtype="auto", k_scale=None, v_scale=None, lse=None, overlap=False,
+                workspace=None):
     """``reshape_and_cache`` (decode form) + ``paged_attention_v1`` in one call; one
     kernel launch for a bf16 cache.  ``key_cache`` / ``value_cache`` are the device
     addresses of the layer's pointer tables (ints), ``slot_m`` the destination byte
     offsets, ``slot_mapping`` the slot ids, ``seq_lens`` the contexts INCLUDING the
-    appended token.  query/out ``[B, H, D]``, key/value ``[B, KVH, D]`` bf16."""
+    appended token.  query/out ``[B, H, D]``, key/value ``[B, KVH, D]`` bf16.
+    ``overlap=True`` lets the launch overlap the previous ``decode_step`` on the
+    stream (VT_STEP_OVERLAP): only for a different layer's ranges, see vtensor.h;
+    pass a private zero-filled ``workspace`` (uint8 tensor) in that case."""
     _require_cuda(out, query, key, value, slot_m, slot_mapping, seq_lens)
     batch, num_heads, head_size = query.shape
     key = key.view(batch, num_kv_heads, head_size)
     value = value.view(batch, num_kv_heads, head_size)
-    ws = attn_workspace(query.device, batch, num_heads, head_size, max_seq_len)
+    if overlap and workspace is None:
+        raise RuntimeError("decode_step(overlap=True) needs a private zero-filled workspace")
+    ws = workspace if workspace is not None else attn_workspace(query.device, batch, num_heads, head_size,
+                                                                max_seq_len)
     with torch.cuda.device(query.device):
         check(lib.vt_decode_step(_ptr(out), out.stride(0), _ptr(query), query.stride(0), _ptr(key), _ptr(value),
                                  key.stride(0), value.stride(0), _ptr(slot_m), c_void_p(int(key_cache)),
                                  c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens), batch, num_heads,
                                  num_kv_heads, head_size, int(max_seq_len), float(scale), _kv_dtype(kv_cache_dtype),
-                                 _ptr(k_scale), _ptr(v_scale), _ptr(lse), _ptr(ws), ws.numel(), _stream()),
+                                 _ptr(k_scale), _ptr(v_scale), _ptr(lse), _ptr(ws), ws.numel(),
+                                 1 if overlap else 0, _stream()),
               "vt_decode_step")
 
 

@@ -240,13 +240,23 @@ int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype
  * call enqueues the append kernel followed by the attention kernels.
  * Replaces the pair of calls in XFormersImpl.forward
  * (vllm/attention/backends/xformers.py:310-312 and :407-430).
- * key / value must be 16-byte aligned with strides that are multiples of 8 elements. */
+ * key / value must be 16-byte aligned with strides that are multiples of 8 elements.
+ *
+ * flags: 0, or VT_STEP_OVERLAP to let this launch overlap the tail of the previous
+ * kernel on the stream when that kernel was a vt_decode_step too (programmatic
+ * dependent launch): this call's CTAs take SM slots as the previous call's CTAs
+ * exit and stream their K/V early.  Only set it when (1) nothing this call reads
+ * — q, key, value, seq_lens, slot_ids, byte_off, the slots' ranges — is written by
+ * the previous kernel on the stream (consecutive LAYERS of one step qualify; two
+ * steps on the same layer do not), and (2) the workspace was zero-filled once
+ * after allocation and is used by nothing but these calls. */
+#define VT_STEP_OVERLAP 1u
 int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *key,
                    const void *value, int64_t key_stride, int64_t value_stride, const int64_t *byte_off,
                    const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
                    const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len, float scale,
                    int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
-                   size_t workspace_bytes, void *stream);
+                   size_t workspace_bytes, unsigned flags, void *stream);
 
 /* vt_decode_attn for callers that cannot allocate device memory at all.
  * (No counterpart in the reference: its attention ops get their scratch from

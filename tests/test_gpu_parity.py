@@ -280,6 +280,59 @@ def test_backend_forward_decode_steps(G, oracle):
         eng.close()
 
 
+@pytest.mark.parametrize("h,kvh", [(8, 1), (8, 8)])
+def test_decode_runner_graph_replay_with_layer_overlap(G, oracle, h, kvh):
+    """DecodeRunner: all layers of a step in one CUDA graph, consecutive layers
+    overlapped with programmatic dependent launch.  Several replays (the graph is
+    captured on the first step), every layer's output and cache rows against the
+    oracle."""
+    from glake_b200.backend import DecodeRunner, VTensorAttentionImpl, VTensorCacheEngine, VTensorMetadata, prepare_step
+    from glake_b200 import ops
+    layers, lens0 = 4, [300, 1, 1500, 65]
+    rs = np.random.RandomState(17 + kvh)
+    eng = VTensorCacheEngine(layers, kvh, 128, len(lens0), 2048)
+    impl = VTensorAttentionImpl(h, 128, SCALE, kvh)
+    holder = G.GpuKV.__new__(G.GpuKV)
+    holder.engine, holder.kvh, holder.fp8, holder.slots = eng, kvh, False, list(range(len(lens0)))
+    try:
+        # context: prefill through the append kernel, layer by layer
+        hist_k = [[synth.normal_bf16(rs, n - 1, kvh, 128) for n in lens0] for _ in range(layers)]
+        hist_v = [[synth.normal_bf16(rs, n - 1, kvh, 128) for n in lens0] for _ in range(layers)]
+        pre = [n - 1 for n in lens0]
+        meta = VTensorMetadata(holder.slots, pre, kvh, 128, num_prefills=len(pre))
+        prepare_step(meta, eng)
+        for l in range(layers):
+            ops.reshape_and_cache(torch.cat(hist_k[l]).cuda(), torch.cat(hist_v[l]).cuda(), eng.k_cache_ptr[l],
+                                  eng.v_cache_ptr[l], meta.slot_m, meta.slot_mapping, meta.seq_lens_tensor,
+                                  meta.cache_seq_lens, max(pre), kvh, 128)
+        runner = DecodeRunner(eng, impl, len(lens0), host_io=True)
+        assert runner.overlap
+        lens = list(pre)
+        for step in range(4):
+            lens = [n + 1 for n in lens]
+            q = synth.normal_bf16(rs, layers, len(lens), h * 128)
+            nk = synth.normal_bf16(rs, layers, len(lens), kvh * 128)
+            nv = synth.normal_bf16(rs, layers, len(lens), kvh * 128)
+            runner.hq.copy_(q), runner.hk.copy_(nk), runner.hv.copy_(nv)
+            runner.step(VTensorMetadata(holder.slots, lens, kvh, 128, num_decode_tokens=len(lens)))
+            runner.synchronize()
+            for l in range(layers):
+                hist_k[l] = [torch.cat([a, b.view(1, kvh, 128)]) for a, b in zip(hist_k[l], nk[l])]
+                hist_v[l] = [torch.cat([a, b.view(1, kvh, 128)]) for a, b in zip(hist_v[l], nv[l])]
+                holder.layer, holder.lens = l, lens
+                for i in range(len(lens)):
+                    assert torch.equal(holder.read_rows(i, "k"), hist_k[l][i])
+                    assert torch.equal(holder.read_rows(i, "v"), hist_v[l][i])
+                r = oracle.fill_ranges(hist_k[l], hist_v[l])
+                port = oracle.port_decode_attn(q[l].view(len(lens), h, 128), r, torch.arange(len(lens)),
+                                               torch.tensor(lens, dtype=torch.int32), kvh, SCALE)
+                ok, err = close_2e3(runner.hout[l].view(len(lens), h, 128), port, ulp_slack=True)
+                assert ok, (step, l, err)
+        assert ops.attn_status() == 0
+    finally:
+        eng.close()
+
+
 def test_full_size_properties_config3_shape(G):
     """BASELINE config 3 shape on one sequence pair (32 q / 8 kv heads, 16k-32k
     tokens), too long for the scalar oracle in seconds, checked through
