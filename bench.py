@@ -34,6 +34,7 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 D = 128
+LOOKAHEAD_ROWS = 64   # decode steps between asking for a chunk and needing it
 WORKLOADS = {
     #  name       layers  B    H   KVH   lo     hi     fp8
     "7b":       (32,    64,  32, 32,  1024,  4096,  False),
@@ -195,6 +196,12 @@ class Job:
                                   max(self.lens), self.kvh, D, self.dtype,
                                   self.scale_k[layer] if fp8 else None, self.scale_v[layer] if fp8 else None)
             del kcat, vcat
+        # prefill-time headroom (the reference maps 100 tokens past the prompt,
+        # vmm_allocator.cpp:322-337): every slot starts with LOOKAHEAD_ROWS rows of room
+        for seg, n in zip(self.engine.vmm_kvcache_segment, self.lens):
+            while seg.actual_size < (n + LOOKAHEAD_ROWS) * row:
+                if not seg.expandMultiSegment(1):
+                    raise RuntimeError("chunk pool exhausted while mapping prefill headroom")
         torch.cuda.synchronize()
         self.setup_s = time.time() - t0
         # per-step inputs: one set per layer, reused every step (values do not matter for timing)
@@ -218,8 +225,9 @@ class Job:
         self.lens = [n + 1 for n in self.lens]
         extend = []
         for slot, seg in zip(self.slots, self.engine.vmm_kvcache_segment):
-            # the scheduler's rule: ask for the next chunk one row before it is needed
-            extend.append(slot if seg.used_size + 2 * row > seg.actual_size and seg.ready() else -1)
+            # the scheduler's rule: ask for the next chunk LOOKAHEAD rows before it is needed, so
+            # that the background mapping (2 x layers driver calls) is long done by then
+            extend.append(slot if seg.used_size + LOOKAHEAD_ROWS * row > seg.actual_size and seg.ready() else -1)
         return self.VTensorMetadata(self.slots, self.lens, self.kvh, D, num_decode_tokens=self.b,
                                     extend_seq_list=extend, kv_elem_size=self.e)
 
@@ -282,15 +290,19 @@ def timed(job, fn, stream, steps, warmup, world, sampler=None):
     lens0 = list(job.lens)
     job.launches = 0
     a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
     if sampler:
         sampler.mark_begin()
     a.record(stream)
-    for _ in range(steps):
+    for i in range(steps):
         fn()
+        marks[i].record(stream)
     z.record(stream)
     torch.cuda.synchronize()
     if sampler:
         sampler.mark_end()
+    per_step = [a.elapsed_time(marks[0])] + [marks[i - 1].elapsed_time(marks[i]) for i in range(1, steps)]
+    job.step_ms = sorted(per_step)
     ms = a.elapsed_time(z)
     if world > 1:
         from glake_b200 import tp
@@ -326,6 +338,11 @@ def run_ours(args):
     ms, attn_b, app_b, launches = timed(job, job.step_resident, job.resident.stream, args.steps, args.warmup, world,
                                         sampler)
     clocks = sampler.stop() if sampler else None
+    step_ms = list(job.step_ms)
+    st = job.A.stats()
+    alloc_stats = {"chunks_total": st["chunks_total"], "chunks_free": st["chunks_free"], "map_calls": st["map_calls"],
+                   "set_access_calls": st["set_access_calls"], "map_seconds": round(st["map_ns"] * 1e-9, 3), "of_which_set_access_seconds": round(st["access_ns"] * 1e-9, 3),
+                   "async_growths": st["async_completed"]}
     attn_ms = job.time_attention_only()
     lens_now = list(job.lens)
     e2e = None
@@ -373,6 +390,9 @@ def run_ours(args):
                    "split_k": {"part_tokens": part, "max_parts": parts, "variant": ["simt split-k", "tensor-core split-k", "tensor-core flat persistent"][variant]},
                    "kv_setup_seconds": round(job.setup_s, 1), "cuda_graph": True, "parallelism": f"tp{world} (heads sharded, no collective in the path)"},
         "tokens_per_s": round(b * args.steps / (ms * 1e-3), 1),
+        "step_ms": {"min": round(step_ms[0], 3), "median": round(step_ms[len(step_ms) // 2], 3),
+                    "max": round(step_ms[-1], 3)},
+        "allocator": alloc_stats,
         "pct_of_nominal_8TBs": round(100 * achieved / 8000.0, 1),
         "gpu_launches": launches,
         "kernel_status": status,

@@ -30,7 +30,7 @@ class VTensorError(RuntimeError):
 class Stats(ctypes.Structure):
     _fields_ = [(n, c_uint64) for n in (
         "chunks_total", "chunks_free", "chunk_bytes", "map_calls", "unmap_calls", "set_access_calls",
-        "map_ns", "async_requests", "async_completed", "async_failed", "segments")]
+        "map_ns", "access_ns", "async_requests", "async_completed", "async_failed", "segments")]
 
 
 def _load():

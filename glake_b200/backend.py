@@ -200,8 +200,12 @@ class DecodeRunner:
         self.k = torch.zeros(layers, batch, kd, dtype=torch.bfloat16, device=dev)
         self.v = torch.zeros(layers, batch, kd, dtype=torch.bfloat16, device=dev)
         self.out = torch.zeros(layers, batch, hd, dtype=torch.bfloat16, device=dev)
-        self.h64 = torch.zeros(2 * batch, dtype=torch.int64).pin_memory()     # byte offsets | slot ids
-        self.h32 = torch.zeros(2 * batch, dtype=torch.int32).pin_memory()     # seq lens | source-row starts
+        # two pinned staging sets used alternately, so that the host can fill step n+1's
+        # integers while step n still runs; each: byte offsets | slot ids, seq lens | row starts
+        self.h64 = [torch.zeros(2 * batch, dtype=torch.int64).pin_memory() for _ in range(2)]
+        self.h32 = [torch.zeros(2 * batch, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.staged = [None, None]   # event recorded after a staging set has been copied to the device
+        self.n_steps = 0
         self.d64 = torch.zeros(2 * batch, dtype=torch.int64, device=dev)
         self.d32 = torch.zeros(2 * batch, dtype=torch.int32, device=dev)
         if host_io:
@@ -213,9 +217,8 @@ class DecodeRunner:
         self.stream = torch.cuda.Stream(device=dev)
 
     def _body(self, meta):
-        """Everything the device does in one step, on the current stream."""
-        self.d64.copy_(self.h64, non_blocking=True)
-        self.d32.copy_(self.h32, non_blocking=True)
+        """Everything the device does in one step after the per-step integers have
+        arrived in d64 / d32, on the current stream."""
         if self.host_io:
             self.q.copy_(self.hq, non_blocking=True)
             self.k.copy_(self.hk, non_blocking=True)
@@ -241,11 +244,19 @@ class DecodeRunner:
         assert len(meta.slot_mapping_list) == self.batch
         slot_m, starts = prepare_step_host(meta, self.engine)
         b = self.batch
-        self.stream.synchronize()   # the previous replay may still be reading the staging buffers
-        self.h64[:b] = torch.tensor(slot_m, dtype=torch.int64)
-        self.h64[b:] = torch.tensor(meta.slot_mapping_list, dtype=torch.int64)
-        self.h32[:b] = torch.tensor(meta.seq_lens, dtype=torch.int32)
-        self.h32[b:] = torch.tensor(starts, dtype=torch.int32)
+        cur = self.n_steps % 2
+        self.n_steps += 1
+        if self.staged[cur] is not None:
+            self.staged[cur].synchronize()   # its copy of two steps ago has long been done
+        self.h64[cur].copy_(torch.tensor(slot_m + list(meta.slot_mapping_list), dtype=torch.int64))
+        self.h32[cur].copy_(torch.tensor(list(meta.seq_lens) + starts, dtype=torch.int32))
+        with torch.cuda.stream(self.stream):
+            # stream-ordered: runs after the previous replay has finished with d64 / d32
+            self.d64.copy_(self.h64[cur], non_blocking=True)
+            self.d32.copy_(self.h32[cur], non_blocking=True)
+            if self.staged[cur] is None:
+                self.staged[cur] = torch.cuda.Event()
+            self.staged[cur].record(self.stream)
         bucket = (meta.max_seq_len + self.BUCKET - 1) // self.BUCKET * self.BUCKET
         graph = self.graphs.get(bucket)
         if graph is None:

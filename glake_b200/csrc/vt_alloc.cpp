@@ -71,7 +71,9 @@ int grow_chunks(vt_seg *seg, size_t n) {
       ++done_maps;
     }
     if (err == CUDA_SUCCESS) {
+      const uint64_t ta = now_ns();
       err = drv->set_access_rw(at, n * cb);
+      pool->access_ns += now_ns() - ta;
       pool->set_access_calls++;
     }
   }
@@ -220,6 +222,7 @@ int vt_pool_stats(vt_pool *pool, vt_stats *out) {
   out->unmap_calls = pool->unmap_calls;
   out->set_access_calls = pool->set_access_calls;
   out->map_ns = pool->map_ns;
+  out->access_ns = pool->access_ns;
   out->async_requests = pool->async_requests;
   out->async_completed = pool->async_completed;
   out->async_failed = pool->async_failed;

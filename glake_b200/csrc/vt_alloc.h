@@ -26,7 +26,7 @@ struct vt_pool {
   bool stop = false;
   std::thread worker;
 
-  std::atomic<uint64_t> map_calls{0}, unmap_calls{0}, set_access_calls{0}, map_ns{0};
+  std::atomic<uint64_t> map_calls{0}, unmap_calls{0}, set_access_calls{0}, map_ns{0}, access_ns{0};
   std::atomic<uint64_t> async_requests{0}, async_completed{0}, async_failed{0};
   std::atomic<int64_t> segments{0}, tables{0};
 };

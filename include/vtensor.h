@@ -67,7 +67,8 @@ typedef struct vt_stats {
   uint64_t chunks_total, chunks_free;
   uint64_t chunk_bytes;
   uint64_t map_calls, unmap_calls, set_access_calls; /* driver calls issued   */
-  uint64_t map_ns;                                   /* wall time spent in them */
+  uint64_t map_ns;                                   /* wall time spent in growth (map + set-access) */
+  uint64_t access_ns;                                /* of which cuMemSetAccess */
   uint64_t async_requests, async_completed, async_failed;
   uint64_t segments;
 } vt_stats;
