@@ -52,8 +52,6 @@ __device__ __forceinline__ unsigned long long gtime() {
 #endif
 
 constexpr int kStages = kMmaStages;
-constexpr int kCWarps = kMmaCWarps;
-constexpr int kThreads = kMmaThreads;
 constexpr int kRing = kStages * kStageB;
 constexpr int kPartRow = kFlatPartRow;   // floats per published (q head, warp) state: O[128], max, sum, pad
 
@@ -96,9 +94,18 @@ __device__ __forceinline__ int owner_of(long long tau, long long total, int n_ct
   return static_cast<int>(((tau + 1) * n_ctas - 1) / total);
 }
 
-template <int NB, int HS, int R>
-__global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
+// W = per-warp engine (WarpAttn: bf16 cache, 4 consumer warps; WarpAttnF8: fp8 e4m3
+// cache, 8 consumer warps), NB = 8-head blocks per kv head, HS = kv heads per CTA,
+// R = consecutive tokens per 1 KiB bulk copy; HS * R = consumer warps.
+template <template <int> class W, int NB, int HS, int R>
+__global__ void __launch_bounds__((W<NB>::kWarps + 1) * 32, (W<NB>::kWarps == 8 && NB == 1) ? 2 : 1)
+attn_flat_kernel(AttnParams p) {
+  constexpr int kCWarps = W<NB>::kWarps;
+  constexpr int kThreads = (kCWarps + 1) * 32;
+  constexpr int kRowB = W<NB>::kRowBytes;
+  constexpr bool kFp8 = kRowB == 128;
   static_assert(HS * R == kCWarps, "one consumer warp per (kv head, row of a group)");
+  static_assert(kCWarps * kRowB == kGroupB, "a group is 1 KiB");
   extern __shared__ __align__(128) unsigned char smem[];
   constexpr int TILE_TOK = kGroupsPerTile * R;
   constexpr int HEADS = NB * 8;
@@ -219,8 +226,8 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
   const int hs = warp % HS, rr = warp / HS;      // kv head within the slab, row within each group
   const uint32_t row_off = (rr * HS + hs) * kRowB;
   const uint32_t k_off = k_lane_offset(lane, row_off), v_off = v_lane_offset(lane, row_off);
-  const float sl2 = p.scale * 1.4426950408889634f;
-  const int tid = threadIdx.x;  // 0..127
+  const float sl2_base = p.scale * 1.4426950408889634f;
+  const int tid = threadIdx.x;  // 0 .. kCWarps * 32 - 1
   __nv_bfloat16 *out = static_cast<__nv_bfloat16 *>(p.out);
 
   // Sequences without context produce zeros; nobody owns a tile of theirs.
@@ -255,7 +262,8 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
         append_v = reinterpret_cast<char *>(p.v_table[slot]);
       }
     }
-    WarpAttn<NB> st;
+    const float sl2 = kFp8 ? sl2_base * p.k_scale[kv_head] : sl2_base;   // fp8: K's scale folded into the logits
+    W<NB> st;
     st.start(static_cast<const __nv_bfloat16 *>(p.q) + pc.b * p.q_stride + kv_head * g * kHeadDim, g, lane);
     for (int tile = pc.tile_begin; tile < pc.tile_end; ++tile, ++it) {
       const int s = it % kStages;
@@ -263,7 +271,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
       if (failed) continue;
       if (it == 0) VT_TR(2);
       const int tok0 = tile * TILE_TOK + rr;      // token of fragment row 0
-      if (append_off >= 0 && (seq_len - 1 - tok0) % R == 0 && seq_len - 1 >= tok0 &&
+      if (!kFp8 && append_off >= 0 && (seq_len - 1 - tok0) % R == 0 && seq_len - 1 >= tok0 &&
           seq_len - 1 < (tile + 1) * TILE_TOK) {
         // Fused step: this warp holds the newest token's row of its kv head; make it
         // part of the cache (8 bytes per lane for K and for V).
@@ -285,19 +293,20 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
     if (R == 1 && whole) {
       // This warp saw every token of its kv head: write the result from registers.
       const int r4 = lane >> 2, c4 = lane & 3;
+      const float vs = kFp8 ? p.v_scale[kv_head] : 1.0f;
 #pragma unroll
       for (int nb = 0; nb < NB; ++nb) {
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int head = nb * 8 + 2 * c4 + e;
           if (head < g) {
-            const float inv = 1.0f / st.lrun[nb][e];   // > 0: a stream holds at least one token
+            const float inv = vs / st.lrun[nb][e];   // sum > 0: a stream holds at least one token
             const int hq = kv_head * g + head;
             __nv_bfloat16 *dst = out + pc.b * p.out_stride + hq * kHeadDim;
 #pragma unroll
             for (int mb = 0; mb < 8; ++mb) {
-              dst[mb * 16 + r4] = __float2bfloat16(st.o[nb][mb][e] * inv);
-              dst[mb * 16 + r4 + 8] = __float2bfloat16(st.o[nb][mb][2 + e] * inv);
+              dst[W<NB>::dim_of(mb, 0, r4)] = __float2bfloat16(st.o[nb][mb][e] * inv);
+              dst[W<NB>::dim_of(mb, 1, r4)] = __float2bfloat16(st.o[nb][mb][2 + e] * inv);
             }
             if (p.lse && r4 == 0)
               p.lse[pc.b * p.h + hq] = (st.mrun[nb][e] + log2f(st.lrun[nb][e])) * 0.6931471805599453f;
@@ -320,23 +329,24 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
         float *mbuf = reinterpret_cast<float *>(smem);          // [kCWarps][HEADS][kPartRow]
         st.template store<kPartRow>(mbuf + warp * HEADS * kPartRow, lane, g);
         named_bar_sync(1, kCWarps * 32);
-        for (int hh = 0; hh < HS; ++hh)
-          for (int head = 0; head < g; ++head) {
-            float M = -INFINITY;
+        // thread -> (head pair index, output dim): 128 dims x (consumer threads / 128) pairs at a time
+        for (int pair = tid >> 7; pair < HS * g; pair += kCWarps * 32 / 128) {
+          const int hh = pair / g, head = pair % g, d = tid & 127;
+          float M = -INFINITY;
 #pragma unroll
-            for (int r = 0; r < R; ++r) M = fmaxf(M, mbuf[((r * HS + hh) * HEADS + head) * kPartRow + 128]);
-            float L = 0.f, O = 0.f;
+          for (int r = 0; r < R; ++r) M = fmaxf(M, mbuf[((r * HS + hh) * HEADS + head) * kPartRow + 128]);
+          float L = 0.f, O = 0.f;
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-              const float *src = mbuf + ((r * HS + hh) * HEADS + head) * kPartRow;
-              const float f = exp2f(src[128] - M);   // M is finite: row 0 of the piece's first tile is valid
-              L = fmaf(f, src[129], L);
-              O = fmaf(f, src[tid], O);
-            }
-            float *dst = slot_base + (hh * HEADS + head) * kPartRow;
-            dst[tid] = O;
-            if (tid == 0) { dst[128] = M; dst[129] = L; }
+          for (int r = 0; r < R; ++r) {
+            const float *src = mbuf + ((r * HS + hh) * HEADS + head) * kPartRow;
+            const float f = exp2f(src[128] - M);   // M is finite: row 0 of the piece's first tile is valid
+            L = fmaf(f, src[129], L);
+            O = fmaf(f, src[d], O);
           }
+          float *dst = slot_base + (hh * HEADS + head) * kPartRow;
+          dst[d] = O;
+          if (d == 0) { dst[128] = M; dst[129] = L; }
+        }
       } else {
         st.template store<kPartRow>(slot_base + warp * HEADS * kPartRow, lane, g);
       }
@@ -421,7 +431,7 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
             }
           }
           const int hq = (pc.slab * HS + hh) * g + head;
-          const float inv = 1.0f / L;
+          const float inv = (kFp8 ? p.v_scale[pc.slab * HS + hh] : 1.0f) / L;
           uint2 packed;
           packed.x = pack_bf16(acc.x * inv, acc.y * inv);
           packed.y = pack_bf16(acc.z * inv, acc.w * inv);
@@ -438,12 +448,13 @@ __global__ void __launch_bounds__(kThreads) attn_flat_kernel(AttnParams p) {
   if (failed && lane == 0) atomicExch(p.status, kKernelErrMagic);
 }
 
-template <int NB, int HS, int R>
+template <template <int> class W, int NB, int HS, int R>
 int launch(const AttnParams &p, cudaStream_t stream) {
+  constexpr int kThreads = (W<NB>::kWarps + 1) * 32;
   const int smem = flat_smem_bytes(p.batch);
   static int configured = 0;
   if (configured < smem) {
-    if (cudaFuncSetAttribute(attn_flat_kernel<NB, HS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+    if (cudaFuncSetAttribute(attn_flat_kernel<W, NB, HS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
       return VT_ERR_CUDA;
     configured = smem;
@@ -459,29 +470,46 @@ int launch(const AttnParams &p, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    return cudaLaunchKernelEx(&cfg, attn_flat_kernel<NB, HS, R>, p) == cudaSuccess ? VT_OK : VT_ERR_CUDA;
+    return cudaLaunchKernelEx(&cfg, attn_flat_kernel<W, NB, HS, R>, p) == cudaSuccess ? VT_OK : VT_ERR_CUDA;
   }
-  attn_flat_kernel<NB, HS, R><<<p.n_ctas, kThreads, smem, stream>>>(p);
+  attn_flat_kernel<W, NB, HS, R><<<p.n_ctas, kThreads, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;
 }
 
 template <int NB>
-int launch_nb(const AttnParams &p, cudaStream_t stream) {
-  if (p.kvh % 4 == 0) return launch<NB, 4, 1>(p, stream);
-  if (p.kvh == 2) return launch<NB, 2, 2>(p, stream);
-  if (p.kvh == 1) return launch<NB, 1, 4>(p, stream);
+int launch_bf16(const AttnParams &p, cudaStream_t stream) {
+  if (p.kvh % 4 == 0) return launch<WarpAttn, NB, 4, 1>(p, stream);
+  if (p.kvh == 2) return launch<WarpAttn, NB, 2, 2>(p, stream);
+  if (p.kvh == 1) return launch<WarpAttn, NB, 1, 4>(p, stream);
+  return VT_ERR_UNSUPPORTED;
+}
+
+template <int NB>
+int launch_fp8(const AttnParams &p, cudaStream_t stream) {
+  if (p.kvh % 8 == 0) return launch<WarpAttnF8, NB, 8, 1>(p, stream);
+  if (p.kvh == 4) return launch<WarpAttnF8, NB, 4, 2>(p, stream);
+  if (p.kvh == 2) return launch<WarpAttnF8, NB, 2, 4>(p, stream);
+  if (p.kvh == 1) return launch<WarpAttnF8, NB, 1, 8>(p, stream);
   return VT_ERR_UNSUPPORTED;
 }
 
 }  // namespace
 
 bool attn_flat_supports(int batch, int h, int kvh, int kv_dtype) {
-  return attn_mma_supports(h, kvh, kv_dtype) && batch <= kFlatMaxBatch;
+  const int g = h / kvh;
+  if (batch > kFlatMaxBatch || !(g <= 8 || g == 16)) return false;
+  if (kv_dtype == VT_KV_BF16) return kvh % 4 == 0 || kvh == 2 || kvh == 1;
+  if (kv_dtype == VT_KV_FP8_E4M3) return kvh % 8 == 0 || kvh == 4 || kvh == 2 || kvh == 1;
+  return false;
 }
+
+int flat_consumer_warps(int kv_dtype) { return kv_dtype == VT_KV_FP8_E4M3 ? 8 : 4; }
 
 int launch_attn_flat(const AttnParams &p, int kv_dtype, cudaStream_t stream) {
   if (!attn_flat_supports(p.batch, p.h, p.kvh, kv_dtype)) return VT_ERR_UNSUPPORTED;
-  return (p.h / p.kvh) <= 8 ? launch_nb<1>(p, stream) : launch_nb<2>(p, stream);
+  const bool nb1 = (p.h / p.kvh) <= 8;
+  if (kv_dtype == VT_KV_FP8_E4M3) return nb1 ? launch_fp8<1>(p, stream) : launch_fp8<2>(p, stream);
+  return nb1 ? launch_bf16<1>(p, stream) : launch_bf16<2>(p, stream);
 }
 
 }  // namespace vt

@@ -49,17 +49,18 @@ size_t attn_workspace_bytes(int batch, int h, int max_parts) {
 static size_t flat_counter_bytes(int batch, int kvh) {
   return (static_cast<size_t>(batch) * kvh * sizeof(unsigned) + 255) / 256 * 256;
 }
-static size_t flat_workspace_bytes(int batch, int h, int kvh, bool worst_case = false) {
+static size_t flat_workspace_bytes(int batch, int h, int kvh, int kv_dtype, bool worst_case = false) {
   const int heads = (!worst_case && (h / kvh) <= 8) ? 8 : 16;
+  const int warps = worst_case ? 8 : flat_consumer_warps(kv_dtype);
   return kStatusBytes + flat_counter_bytes(batch, kvh) +
-         static_cast<size_t>(kFlatMaxCtas) * 2 * 4 * heads * kFlatPartRow * sizeof(float);
+         static_cast<size_t>(kFlatMaxCtas) * 2 * warps * heads * kFlatPartRow * sizeof(float);
 }
 
 size_t attn_workspace_bound(int batch, int h, int max_seq_len) {
   const int parts = std::max(1, (max_seq_len + kMinPartTokens - 1) / kMinPartTokens);
   // the flat schedule's scratch does not depend on the context length; h stands in
   // for the kv-head count (its upper bound) when sizing the ticket counters
-  return std::max(attn_workspace_bytes(batch, h, parts), flat_workspace_bytes(batch, h, h, true));
+  return std::max(attn_workspace_bytes(batch, h, parts), flat_workspace_bytes(batch, h, h, VT_KV_BF16, true));
 }
 
 void carve_workspace(void *ws, int batch, int h, int max_parts, AttnParams *p) {
@@ -127,7 +128,7 @@ int plan_attn(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_
   plan->ws_bytes = attn_workspace_bytes(batch, h, plan->max_parts);
   if (plan->variant == 2) {
     plan->max_parts = 1;   // no merge kernel: the last CTA of a stream merges it
-    plan->ws_bytes = flat_workspace_bytes(batch, h, kvh);
+    plan->ws_bytes = flat_workspace_bytes(batch, h, kvh, kv_dtype);
   }
   return VT_OK;
 }
@@ -203,15 +204,18 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
   p.batch = batch; p.h = h; p.kvh = kvh; p.scale = scale; p.k_scale = k_scale; p.v_scale = v_scale;
   p.lse = lse; p.part_tokens = plan.part_tokens; p.max_parts = plan.max_parts;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (new_key && plan.variant != 2) {
+  const bool fused = new_key && plan.variant == 2 && kv_dtype == VT_KV_BF16;
+  if (new_key && !fused) {
     // no fused kernel for this shape / dtype: append first, then attend
     int st = vt_append(new_key, new_value, new_key_stride, new_value_stride, k_table, v_table, byte_off, slot_ids,
                        nullptr, nullptr, 1, batch, kvh, d, kv_dtype, k_scale, v_scale, stream);
     if (st != VT_OK) return st;
   }
   if (plan.variant == 2) {
-    p.new_key = new_key; p.new_value = new_value;
-    p.new_key_stride = new_key_stride; p.new_value_stride = new_value_stride; p.byte_off = byte_off;
+    if (fused) {
+      p.new_key = new_key; p.new_value = new_value;
+      p.new_key_stride = new_key_stride; p.new_value_stride = new_value_stride; p.byte_off = byte_off;
+    }
     vt::carve_flat(workspace, batch, kvh, &p);
     p.n_ctas = vt::flat_grid();
 #ifdef VT_TRACE

@@ -67,6 +67,7 @@ int launch_attn_mma(const AttnParams &p, int kv_dtype, cudaStream_t stream);
 bool attn_mma_supports(int h, int kvh, int kv_dtype);
 int launch_attn_flat(const AttnParams &p, int kv_dtype, cudaStream_t stream);
 bool attn_flat_supports(int batch, int h, int kvh, int kv_dtype);
+int flat_consumer_warps(int kv_dtype);
 int launch_attn_reduce(const AttnParams &p, int kv_dtype, cudaStream_t stream);
 
 }  // namespace vt

@@ -162,9 +162,15 @@ def test_append_strided_source_padding_and_growth_keeps_data(G, oracle):
         eng.close()
 
 
-@pytest.mark.parametrize("h,kvh", [(8, 8), (32, 8)])
-def test_fp8_kv_cache(G, oracle, h, kvh):
-    lens = [520, 2100, 64]
+@pytest.mark.parametrize("h,kvh", [(8, 8), (32, 8), (8, 1), (16, 2), (16, 4), (16, 1), (3, 3)])
+@pytest.mark.parametrize("mode", ["auto", "simt"])
+def test_fp8_kv_cache(G, oracle, monkeypatch, h, kvh, mode):
+    """fp8 e4m3 cache on the tensor-core flat schedule (f16 MMAs) and on the SIMT
+    split-K kernel, every head-group shape incl. the ones that pack several token
+    rows into one bulk copy."""
+    if mode != "auto":
+        monkeypatch.setenv("VT_ATTN_VARIANT", mode)
+    lens = [520, 2100, 64, 1, 129]
     q, k, v = synth.make_case(40 + kvh, lens, h, kvh)
     from glake_b200 import ops
     ks = ops.kv_scales(torch.cat(k).cuda(), kvh, 128)
@@ -179,10 +185,13 @@ def test_fp8_kv_cache(G, oracle, h, kvh):
             assert torch.equal(kv8.read_rows(i, "v"), r8.v_rows(i, n, kvh, 128, fp8=True))
         o8 = kv8.attend(q, SCALE)
         o16 = kv16.attend(q, SCALE)
-        assert (o8.float() - o16.float()).abs().max() <= 3e-2
-        port8 = oracle.port_decode_attn(q, r8, torch.arange(3), torch.tensor(lens, dtype=torch.int32), kvh, SCALE,
-                                        ks.cpu(), vs.cpu())
-        assert (o8.float() - port8.float()).abs().max() <= 1e-2   # the reference's own fp8 tolerance
+        long_ctx = [i for i, n in enumerate(lens) if n >= 512]
+        assert (o8.float() - o16.float())[long_ctx].abs().max() <= 3e-2
+        port8 = oracle.port_decode_attn(q, r8, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32), kvh,
+                                        SCALE, ks.cpu(), vs.cpu())
+        # the reference's own fp8 tolerance (1e-2), or two bf16 ulps where short contexts make outputs O(1)
+        err = (o8.float() - port8.float()).abs()
+        assert bool((err <= torch.maximum(torch.full_like(err, 1e-2), port8.float().abs() * 2.0 ** -6)).all())
     finally:
         kv8.close()
         kv16.close()
