@@ -323,6 +323,22 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
                           key, value, key_stride, value_stride, byte_off, flags);
 }
 
+int vt_prefill_attn(void *out, int64_t out_stride, const void *q, int64_t q_stride, const uint64_t *k_table,
+                    const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
+                    const int32_t *q_lens, const int32_t *q_start, int batch, int h, int kvh, int d,
+                    int max_q_len, float scale, int kv_dtype, uint32_t *status, void *stream) {
+  if (batch < 0 || h <= 0 || kvh <= 0 || max_q_len < 0) return VT_ERR_INVALID;
+  if (batch == 0 || max_q_len == 0) return VT_OK;
+  if (!out || !q || !k_table || !v_table || !slot_ids || !seq_lens || !q_lens || !q_start) return VT_ERR_INVALID;
+  if (d != vt::kHeadDim || h % kvh != 0 || kv_dtype != VT_KV_BF16) return VT_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(out) & 3) || (q_stride % 2) || (out_stride % 2))
+    return VT_ERR_INVALID;
+  if (q_stride < static_cast<int64_t>(h) * d || out_stride < static_cast<int64_t>(h) * d) return VT_ERR_INVALID;
+  vt::PrefillParams p{out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, q_lens, q_start,
+                      batch, h, kvh, scale, status};
+  return vt::launch_prefill_attn(p, max_q_len, static_cast<cudaStream_t>(stream));
+}
+
 int vt_decode_attn_status(void *workspace, void *stream, int *code) {
   if (!workspace || !code) return VT_ERR_INVALID;
   uint32_t word = 0;

@@ -51,6 +51,20 @@ constexpr int kFlatMaxBatch = 1024;   // prefix table of the flat schedule lives
 constexpr int kFlatPartRow = 132;     // floats per published piece state row (16-byte aligned)
 constexpr int kFlatMaxCtas = 320;     // 2 per SM on up to 160 SMs
 
+struct PrefillParams {
+  void *out; int64_t out_stride;      // bf16 [tokens, h, 128]; stride of a token row in elements
+  const void *q; int64_t q_stride;
+  const uint64_t *k_table, *v_table;
+  const int64_t *slot_ids;
+  const int32_t *seq_lens;            // context INCLUDING the new tokens
+  const int32_t *q_lens;              // new tokens per entry
+  const int32_t *q_start;             // first row of the entry in q / out
+  int batch, h, kvh;
+  float scale;
+  uint32_t *status;                   // optional status word
+};
+int launch_prefill_attn(const PrefillParams &p, int max_q_len, cudaStream_t stream);
+
 struct AttnPlan {
   int part_tokens, max_parts;
   int variant;       // 0 = SIMT split-K, 1 = tensor-core split-K, 2 = tensor-core flat schedule

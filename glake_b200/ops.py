@@ -145,8 +145,20 @@ def fwd_kvcache(q, k_table_ptr, v_table_ptr, max_seq_len, num_kv_heads, batch, s
             raise RuntimeError(f"fwd_kvcache: {name} is not supported on the vTensor path")
     if window_left != -1 or window_right != -1:
         raise RuntimeError("fwd_kvcache: sliding window is not supported")
-    if q.dim() != 4 or q.shape[1] != 1:
-        raise RuntimeError("fwd_kvcache: decode call expects q of shape [B, 1, H, D]")
+    if q.dim() != 4:
+        raise RuntimeError("fwd_kvcache: q must be [B, S, H, D]")
+    if q.shape[1] != 1:
+        # prefix-extend form (xformers.py:362-385): S new tokens per sequence, causal over the range
+        if _kv_dtype(kv_cache_dtype) != VT_KV_BF16 or not causal:
+            raise RuntimeError("fwd_kvcache: seqlen_q > 1 needs a bf16 cache and causal=True")
+        b, s, h, d = q.shape
+        qc = q.contiguous().view(b * s, h, d)
+        o = out if out is not None else torch.empty(b, s, h, d, dtype=q.dtype, device=q.device)
+        q_lens = torch.full((b,), s, dtype=torch.int32, device=q.device)
+        q_start = torch.arange(b, dtype=torch.int32, device=q.device) * s
+        prefill_attention(o.view(b * s, h, d), qc, k_table_ptr, v_table_ptr, num_kv_heads, softmax_scale,
+                          slot_mapping, seq_lens, q_lens, q_start, s)
+        return o, None
     b, _, h, d = q.shape
     q3 = q.view(b, h, d) if q.is_contiguous() else q[:, 0]
     o = out if out is not None else torch.empty(b, 1, h, d, dtype=q.dtype, device=q.device)
@@ -183,6 +195,23 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
                                  _ptr(k_scale), _ptr(v_scale), _ptr(lse), _ptr(ws), ws.numel(),
                                  1 if overlap else 0, _stream()),
               "vt_decode_step")
+
+
+def prefill_attention(out, query, key_cache, value_cache, num_kv_heads, scale, slot_mapping, seq_lens, q_lens,
+                      q_start, max_q_len):
+    """Causal attention of the new tokens over the slots' whole ranges (the new rows
+    already appended with ``reshape_and_cache``).  query/out ``[tokens, H, D]`` bf16,
+    ``key_cache`` / ``value_cache`` the pointer-table addresses (ints), ``seq_lens``
+    the contexts including the new tokens, ``q_lens`` / ``q_start`` int32 per entry."""
+    _require_cuda(out, query, slot_mapping, seq_lens, q_lens, q_start)
+    if query.dtype != torch.bfloat16:
+        raise RuntimeError("prefill_attention: bf16 only")
+    n, num_heads, head_size = query.shape
+    with torch.cuda.device(query.device):
+        check(lib.vt_prefill_attn(_ptr(out), out.stride(0), _ptr(query), query.stride(0), c_void_p(int(key_cache)),
+                                  c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens), _ptr(q_lens),
+                                  _ptr(q_start), slot_mapping.numel(), num_heads, num_kv_heads, head_size,
+                                  int(max_q_len), float(scale), VT_KV_BF16, None, _stream()), "vt_prefill_attn")
 
 
 def attn_plan(batch, num_heads, num_kv_heads, max_seq_len, kv_cache_dtype="auto", num_splits=0):

@@ -259,6 +259,23 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
                    int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
                    size_t workspace_bytes, unsigned flags, void *stream);
 
+/* Causal attention of the NEW tokens of each sequence over its whole range
+ * (prefix + new tokens; the new rows must have been appended with vt_append):
+ * query row j of entry i sits at position seq_lens[i] - q_lens[i] + j and attends
+ * tokens [0, position].  Replaces the prefix-prefill call of fwd_kvcache with
+ * seqlen_q > 1 (vllm/attention/backends/xformers.py:362-385).
+ *   out, q      bf16 [tokens, h, d]; stride of a token row in elements
+ *   seq_lens    device int32 [batch]: context INCLUDING the new tokens
+ *   q_lens      device int32 [batch]: new tokens per entry (<= seq_lens)
+ *   q_start     device int32 [batch]: first row of entry i in q / out
+ *   max_q_len   host upper bound of q_lens (sizes the grid)
+ *   status      optional device word set to a non-zero magic if a bounded wait ran out; may be NULL
+ * bf16 KV only; d must be 128. */
+int vt_prefill_attn(void *out, int64_t out_stride, const void *q, int64_t q_stride, const uint64_t *k_table,
+                    const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
+                    const int32_t *q_lens, const int32_t *q_start, int batch, int h, int kvh, int d,
+                    int max_q_len, float scale, int kv_dtype, uint32_t *status, void *stream);
+
 /* vt_decode_attn for callers that cannot allocate device memory at all.
  * (No counterpart in the reference: its attention ops get their scratch from
  * torch's allocator.)

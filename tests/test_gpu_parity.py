@@ -342,6 +342,52 @@ def test_decode_runner_graph_replay_with_layer_overlap(G, oracle, h, kvh):
         eng.close()
 
 
+@pytest.mark.parametrize("h,kvh", [(4, 4), (8, 2), (8, 1)])
+def test_prefill_attention_over_the_range(G, oracle, h, kvh):
+    """Prefix-extend: the new tokens' causal attention over prefix + new tokens,
+    through vt_prefill_attn, against the oracle; ragged q_lens incl. tile edges
+    (63/64/65), empty prefix and long prefix; then the padded fwd_kvcache form."""
+    from glake_b200 import ops
+    lens = [1, 64, 65, 200, 331, 700]          # total context per sequence
+    q_lens = [1, 64, 63, 200, 31, 130]         # of which new
+    _, k, v = synth.make_case(600 + h + kvh, lens, h, kvh)
+    rs = np.random.RandomState(8)
+    kv = G.GpuKV(k, v, kvh)
+    try:
+        starts = np.concatenate([[0], np.cumsum(q_lens)[:-1]]).astype(np.int32)
+        q = synth.normal_bf16(rs, int(sum(q_lens)), h, 128)
+        out = torch.empty_like(q, device="cuda")
+        ql = torch.tensor(q_lens, dtype=torch.int32)
+        qs = torch.from_numpy(starts)
+        ops.prefill_attention(out, q.cuda(), kv.k_table, kv.v_table, kvh, SCALE, kv.meta.slot_mapping,
+                              kv.meta.seq_lens_tensor, ql.cuda(), qs.cuda(), max(q_lens))
+        torch.cuda.synchronize()
+        r = oracle.fill_ranges(k, v)
+        port = oracle.port_prefill_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32), ql, qs,
+                                        kvh, SCALE)
+        ok, err = close_2e3(out.cpu(), port, ulp_slack=True)
+        assert ok, err
+        # padded form: every sequence extends by the same 16 tokens
+        s_new = 16
+        lens2 = [n for n in lens if n >= s_new]
+        idx = [i for i, n in enumerate(lens) if n >= s_new]
+        qp = synth.normal_bf16(rs, len(idx), s_new, h, 128)
+        slots = kv.meta.slot_mapping[idx].contiguous()
+        sl = kv.meta.seq_lens_tensor[idx].contiguous()
+        o2, _ = ops.fwd_kvcache(qp.cuda(), kv.k_table, kv.v_table, max(lens2), kvh, len(idx), slots, None, None, sl,
+                                None, None, None, None, None, None, SCALE, True, -1, -1, None, 4)
+        torch.cuda.synchronize()
+        r2 = oracle.fill_ranges([k[i] for i in idx], [v[i] for i in idx])
+        port2 = oracle.port_prefill_attn(qp.view(-1, h, 128), r2, torch.arange(len(idx)),
+                                         torch.tensor(lens2, dtype=torch.int32),
+                                         torch.full((len(idx),), s_new, dtype=torch.int32),
+                                         torch.arange(len(idx), dtype=torch.int32) * s_new, kvh, SCALE)
+        ok, err = close_2e3(o2.cpu().view(-1, h, 128), port2, ulp_slack=True)
+        assert ok, err
+    finally:
+        kv.close()
+
+
 def test_full_size_properties_config3_shape(G):
     """BASELINE config 3 shape on one sequence pair (32 q / 8 kv heads, 16k-32k
     tokens), too long for the scalar oracle in seconds, checked through
