@@ -62,7 +62,7 @@ WORKLOAD_TEXT = {
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=40)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto")
@@ -418,7 +418,10 @@ def load_traffic(name, algorithmic_bytes_per_launch):
     case; traffic grows in proportion to the tokens read) times this launch's
     algorithmic bytes.  null when no capture covers the workload."""
     try:
-        t = json.load(open(os.path.join(ROOT, "profiles", "traffic.json"))).get(name)
+        table = json.load(open(os.path.join(ROOT, "profiles", "traffic.json")))
+        t = table.get(name)
+        if t is None and name == "70b" and int(os.environ.get("WORLD_SIZE", "1")) == 8:
+            t = table.get("70b-tp8")      # the 8-rank share of the 70B workload is that capture's kernel
         return int(t["ratio"] * algorithmic_bytes_per_launch) if t else None
     except (OSError, ValueError, KeyError, TypeError):
         return None
