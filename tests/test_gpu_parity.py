@@ -388,6 +388,68 @@ def test_prefill_attention_over_the_range(G, oracle, h, kvh):
         kv.close()
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_flat_schedule_random_batches(G, oracle, seed):
+    """Randomised batches for the persistent flat schedule: piece boundaries, stream
+    merges, empty sequences, fewer tiles than CTAs, more sequences than the
+    shared-memory base cache holds (> 256), every (kv heads per CTA, rows per copy)
+    shape, bf16 and fp8; fused step and plain attention must agree with the oracle."""
+    from glake_b200 import ops
+    from glake_b200.backend import VTensorMetadata, prepare_step
+    rs = np.random.RandomState(1000 + seed)
+    kvh = int(rs.choice([1, 2, 4, 8, 12]))
+    g = int(rs.choice([1, 2, 4, 8])) if kvh != 12 else 1
+    h = kvh * g
+    fp8 = bool(seed % 3 == 2) and kvh != 12
+    if seed == 5:
+        batch, hi = 300, 40                   # many short sequences
+    elif seed == 7:
+        batch, hi = 3, 20000                  # few long ones: streams cut into many pieces
+    else:
+        batch, hi = int(rs.randint(1, 40)), int(rs.choice([3, 70, 700, 3000]))
+    lens = [int(x) for x in rs.randint(1, hi + 1, size=batch)]
+    q, k, v = synth.make_case(2000 + seed, lens, h, kvh)
+    ks = vs = None
+    if fp8:
+        ks = ops.kv_scales(torch.cat(k).cuda(), kvh, 128)
+        vs = ops.kv_scales(torch.cat(v).cuda(), kvh, 128)
+    kv = G.GpuKV(k, v, kvh, fp8=fp8, k_scale=ks, v_scale=vs)
+    try:
+        out, lse = kv.attend(q, SCALE, return_lse=True)
+        if fp8:
+            r = oracle.fill_ranges(k, v, k_scale=ks.cpu(), v_scale=vs.cpu())
+            port, plse = oracle.port_decode_attn(q, r, torch.arange(batch), torch.tensor(lens, dtype=torch.int32), kvh,
+                                                 SCALE, ks.cpu(), vs.cpu(), return_lse=True)
+            err = (out.float() - port.float()).abs()
+            # The oracle rounds every dequantised K/V element to bf16 as the reference does, the
+            # kernel keeps fp8 * scale exact; on contexts of a few dozen tokens that alone moves
+            # outputs by ~1e-2, so these random cases use the fp8 contract tolerance (3e-2).
+            tol = torch.maximum(torch.full_like(err, 3e-2), port.float().abs() * 2.0 ** -6)
+            worst = int((err - tol).argmax())
+            assert bool((err <= tol).all()), (float(err.flatten()[worst]), float(port.float().flatten()[worst]), lens)
+            assert torch.allclose(lse, plse, atol=2e-2)
+        else:
+            r = oracle.fill_ranges(k, v)
+            port, plse = oracle.port_decode_attn(q, r, torch.arange(batch), torch.tensor(lens, dtype=torch.int32), kvh,
+                                                 SCALE, return_lse=True)
+            ok, err = close_2e3(out, port, ulp_slack=True)
+            assert ok, err
+            assert torch.allclose(lse, plse, atol=2e-3)
+            # same batch with some sequences emptied: zeros there, others unchanged
+            if batch >= 3:
+                sl = kv.meta.seq_lens_tensor.clone()
+                kv.meta.seq_lens_tensor[::3] = 0
+                out2 = kv.attend(q, SCALE)
+                kv.meta.seq_lens_tensor.copy_(sl)
+                assert torch.equal(out2[::3], torch.zeros_like(out2[::3]))
+                keep = [i for i in range(batch) if i % 3]
+                # the tile list is cut differently now, so sums associate differently: equal up to rounding
+                ok, err = close_2e3(out2[keep], out[keep], ulp_slack=True)
+                assert ok, err
+    finally:
+        kv.close()
+
+
 def test_full_size_properties_config3_shape(G):
     """BASELINE config 3 shape on one sequence pair (32 q / 8 kv heads, 16k-32k
     tokens), too long for the scalar oracle in seconds, checked through
