@@ -215,26 +215,52 @@ class DecodeRunner:
         self.workspace = None   # private scratch: the overlapped launches need it zero-filled and to themselves
         self.kernel_launches_per_step = 0
         self.stream = torch.cuda.Stream(device=dev)
+        if host_io:
+            self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+            self.ev_in = [torch.cuda.Event() for _ in range(layers)]
+            self.ev_out = [torch.cuda.Event() for _ in range(layers)]
+            per_layer = batch * (hd + 2 * kd) * 2
+            self.io_group = max(1, min(layers, -(-(1 << 20) // per_layer)))   # >= 1 MiB per host->device copy
 
     def _body(self, meta):
         """Everything the device does in one step after the per-step integers have
         arrived in d64 / d32, on the current stream."""
-        if self.host_io:
-            self.q.copy_(self.hq, non_blocking=True)
-            self.k.copy_(self.hk, non_blocking=True)
-            self.v.copy_(self.hv, non_blocking=True)
+        main = torch.cuda.current_stream()
         b = self.batch
-        for layer in range(self.engine.num_layers):
+        n_layers = self.engine.num_layers
+        if self.host_io:
+            # Host q/k/v travel layer by layer on a side stream, one layer ahead of the
+            # kernels, and each layer's output leaves on another as soon as it exists, so
+            # the PCIe time hides behind the attention kernels instead of bracketing them.
+            self.s_in.wait_stream(main)
+            self.s_out.wait_stream(main)
+            grp = self.io_group   # layers per copy, so that every transfer is worth a DMA launch
+            with torch.cuda.stream(self.s_in):
+                for l0 in range(0, n_layers, grp):
+                    self.q[l0:l0 + grp].copy_(self.hq[l0:l0 + grp], non_blocking=True)
+                    self.k[l0:l0 + grp].copy_(self.hk[l0:l0 + grp], non_blocking=True)
+                    self.v[l0:l0 + grp].copy_(self.hv[l0:l0 + grp], non_blocking=True)
+                    self.ev_in[l0].record(self.s_in)
+        for layer in range(n_layers):
             kc, vc = self.engine.gpu_cache[layer]
             ks = self.k_scale[layer] if self.k_scale is not None else None
             vs = self.v_scale[layer] if self.v_scale is not None else None
+            if self.host_io and layer % self.io_group == 0:
+                main.wait_event(self.ev_in[layer])
             ops.decode_step(self.out[layer].view(b, self.impl.num_heads, self.impl.head_size),
                             self.q[layer].view(b, self.impl.num_heads, self.impl.head_size), self.k[layer],
                             self.v[layer], kc.vmm_ptr, vc.vmm_ptr, self.d64[:b], self.d64[b:], self.d32[:b],
                             meta.max_seq_len, self.impl.num_kv_heads, self.impl.scale, self.impl.kv_cache_dtype,
                             ks, vs, overlap=self.overlap and layer > 0, workspace=self.workspace)
+            if self.host_io and ((layer + 1) % self.io_group == 0 or layer == n_layers - 1):
+                l0 = layer - layer % self.io_group
+                self.ev_out[layer].record(main)
+                self.s_out.wait_event(self.ev_out[layer])
+                with torch.cuda.stream(self.s_out):
+                    self.hout[l0:layer + 1].copy_(self.out[l0:layer + 1], non_blocking=True)
         if self.host_io:
-            self.hout.copy_(self.out, non_blocking=True)
+            main.wait_stream(self.s_in)
+            main.wait_stream(self.s_out)
 
     def step(self, meta: VTensorMetadata):
         """Runs one decode step for ``meta`` (slot ids and context lengths as lists).
