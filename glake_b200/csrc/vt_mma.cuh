@@ -320,7 +320,7 @@ struct WarpAttnF8 {
     }
     // ---- online softmax ----
     const bool v0 = r4 < n_rows, v1 = r4 + 8 < n_rows;
-    uint32_t pb[NB][2], pl[NB][2];
+    uint32_t pb[NB][2];
     bool any_up = false;
     float fac[NB][2];
 #pragma unroll
@@ -342,13 +342,10 @@ struct WarpAttnF8 {
       const float p00 = exp2f(s00 - mn0), p01 = exp2f(s01 - mn1), p10 = exp2f(s10 - mn0), p11 = exp2f(s11 - mn1);
       lrun[nb][0] = lrun[nb][0] * fac[nb][0] + p00 + p10;
       lrun[nb][1] = lrun[nb][1] * fac[nb][1] + p01 + p11;
-      const uint32_t h0 = pack_f16(p00, p01), h1 = pack_f16(p10, p11);
-      const uint32_t l0 = pack_f16(p00 - f16_lo(h0), p01 - f16_hi(h0));
-      const uint32_t l1 = pack_f16(p10 - f16_lo(h1), p11 - f16_hi(h1));
-      pb[nb][0] = movmatrix_trans(h0);
-      pb[nb][1] = movmatrix_trans(h1);
-      pl[nb][0] = movmatrix_trans(l0);
-      pl[nb][1] = movmatrix_trans(l1);
+      // f16 probabilities carry 11 mantissa bits: ample next to the 3-bit mantissa of
+      // the e4m3 values they weigh, so no hi + lo split here.
+      pb[nb][0] = movmatrix_trans(pack_f16(p00, p01));
+      pb[nb][1] = movmatrix_trans(pack_f16(p10, p11));
     }
     if (__any_sync(0xffffffffu, any_up)) {
 #pragma unroll
@@ -379,10 +376,7 @@ struct WarpAttnF8 {
         a[2] = e4m3x2_to_f16x2(prmt(w2[w], w3[w], lo));
         a[3] = e4m3x2_to_f16x2(prmt(w2[w], w3[w], hi));
 #pragma unroll
-        for (int nb = 0; nb < NB; ++nb) {
-          mma_f16(o[nb][mb], a, pb[nb][0], pb[nb][1]);
-          mma_f16(o[nb][mb], a, pl[nb][0], pl[nb][1]);
-        }
+        for (int nb = 0; nb < NB; ++nb) mma_f16(o[nb][mb], a, pb[nb][0], pb[nb][1]);
       }
     }
   }
