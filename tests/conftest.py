@@ -10,6 +10,13 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu)")
+    # The package refuses to import without its CUDA library (there is no fallback), so
+    # build it when the tree is fresh; nvcc cross-compiles for sm_100a without a GPU.
+    so = os.path.join(ROOT, "glake_b200", "libvtensor.so")
+    if not os.path.isfile(so):
+        import subprocess
+        subprocess.check_call(["make", "-C", os.path.join(ROOT, "glake_b200", "csrc"), "-j8"],
+                              stdout=subprocess.DEVNULL)
 
 
 @pytest.fixture(scope="session")
