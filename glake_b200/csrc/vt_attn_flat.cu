@@ -452,13 +452,8 @@ template <template <int> class W, int NB, int HS, int R>
 int launch(const AttnParams &p, cudaStream_t stream) {
   constexpr int kThreads = (W<NB>::kWarps + 1) * 32;
   const int smem = flat_smem_bytes(p.batch);
-  static int configured = 0;
-  if (configured < smem) {
-    if (cudaFuncSetAttribute(attn_flat_kernel<W, NB, HS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-        cudaSuccess)
-      return VT_ERR_CUDA;
-    configured = smem;
-  }
+  static SmemOptIn opt_in;
+  if (!opt_in.ensure(attn_flat_kernel<W, NB, HS, R>, smem)) return VT_ERR_CUDA;
   if (p.overlap) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(p.n_ctas);

@@ -175,13 +175,8 @@ __global__ void __launch_bounds__(kThreads) attn_mma_kernel(AttnParams p) {
 template <int NB, int HS, int R>
 int launch(const AttnParams &p, cudaStream_t stream) {
   constexpr int SMEM = smem_bytes<NB>();
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(attn_mma_kernel<NB, HS, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) !=
-        cudaSuccess)
-      return VT_ERR_CUDA;
-    configured = true;
-  }
+  static SmemOptIn opt_in;
+  if (!opt_in.ensure(attn_mma_kernel<NB, HS, R>, SMEM)) return VT_ERR_CUDA;
   dim3 grid(p.kvh / HS, p.max_parts, p.batch);
   attn_mma_kernel<NB, HS, R><<<grid, kThreads, SMEM, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;

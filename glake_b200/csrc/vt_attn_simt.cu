@@ -258,13 +258,8 @@ __global__ void __launch_bounds__(kThreads) attn_simt_kernel(AttnParams p) {
 template <int G, bool FP8>
 int launch(const AttnParams &p, cudaStream_t stream) {
   constexpr int SMEM = smem_bytes<G, FP8>();
-  static bool configured = false;  // per process; the attribute is per function, any device
-  cudaError_t e = cudaSuccess;
-  if (!configured) {
-    e = cudaFuncSetAttribute(attn_simt_kernel<G, FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    if (e != cudaSuccess) return VT_ERR_CUDA;
-    configured = true;
-  }
+  static SmemOptIn opt_in;
+  if (!opt_in.ensure(attn_simt_kernel<G, FP8>, SMEM)) return VT_ERR_CUDA;
   dim3 grid(p.kvh * ((p.h / p.kvh) / G), p.max_parts, p.batch);
   attn_simt_kernel<G, FP8><<<grid, kThreads, SMEM, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;

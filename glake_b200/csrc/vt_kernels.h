@@ -4,7 +4,25 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include <atomic>
+
 namespace vt {
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) is per device: remembers, per
+// kernel instantiation (one static instance each) and device, the size already set.
+struct SmemOptIn {
+  std::atomic<int> set[64];
+  SmemOptIn() { for (auto &x : set) x.store(0); }
+  template <typename K>
+  bool ensure(K kernel, int bytes) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+    if (set[dev].load(std::memory_order_relaxed) >= bytes) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    set[dev].store(bytes, std::memory_order_relaxed);
+    return true;
+  }
+};
 
 struct AppendParams {
   const void *key, *value;

@@ -239,12 +239,8 @@ __global__ void __launch_bounds__(kPfThreads) prefill_attn_kernel(PrefillParams 
 }  // namespace
 
 int launch_prefill_attn(const PrefillParams &p, int max_q_len, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    if (cudaFuncSetAttribute(prefill_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmem) != cudaSuccess)
-      return VT_ERR_CUDA;
-    configured = true;
-  }
+  static SmemOptIn opt_in;
+  if (!opt_in.ensure(prefill_attn_kernel, kPfSmem)) return VT_ERR_CUDA;
   dim3 grid((max_q_len + kBM - 1) / kBM, p.h, p.batch);
   prefill_attn_kernel<<<grid, kPfThreads, kPfSmem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;

@@ -451,7 +451,7 @@ def test_flat_schedule_random_batches(G, oracle, seed):
 
 
 def test_full_size_properties_config3_shape(G):
-    """BASELINE config 3 shape on one sequence pair (32 q / 8 kv heads, 16k-32k
+    """The long-context GQA shape at full length, one sequence pair (32 q / 8 kv heads, 16k-32k
     tokens), too long for the scalar oracle in seconds, checked through
     size-independent properties: (1) V == 1 everywhere -> every output is 1;
     (2) V[t] = e_(t mod 128) and K == 0 -> uniform softmax, output[d] = count_d / L;
