@@ -6,7 +6,7 @@ from glake_b200 import ops, vmmAllocator as A
 from glake_b200._lib import check, lib
 from glake_b200.backend import VTensorCacheEngine, VTensorMetadata, prepare_step
 
-POOL_CHUNKS = 3072  # 6 GiB of 2 MiB chunks, shared by the whole test session
+POOL_CHUNKS = 4096  # 8 GiB of 2 MiB chunks, shared by the whole test session
 
 
 def ensure_pool():

@@ -487,6 +487,54 @@ def test_full_size_properties_config3_shape(G):
         kv.close()
 
 
+@pytest.mark.parametrize("name,batch,h,kvh,lo,hi,fp8", [
+    ("7b-layer", 64, 32, 32, 1024, 4096, False),
+    ("70b-share-tp2", 64, 32, 4, 4096, 16384, False),
+    ("70b-share-tp8", 64, 8, 1, 4096, 16384, False),
+    ("gqa-fp8", 128, 32, 8, 2048, 8192, True),
+])
+def test_full_size_properties_of_the_bench_shapes(G, name, batch, h, kvh, lo, hi, fp8):
+    """One layer of every benchmark shape at FULL size (up to 2.6 GB of KV), where
+    the scalar oracle would take minutes: K == 0 makes the softmax uniform, and V
+    one-hot in (t mod 128) turns the output into a histogram of the tokens read,
+    output[d] = |{t < L : t mod 128 == d}| / L, exact only if every token of every
+    sequence is read exactly once across tiles, pieces and merges; V == 1 with random
+    K checks the normalisation (every output is 1)."""
+    from glake_b200 import ops
+    g = torch.Generator().manual_seed(77)
+    lens = torch.randint(lo, hi + 1, (batch,), generator=g).tolist()
+    dev = "cuda"
+    ks = vs = None
+    if fp8:
+        ks = torch.ones(kvh, device=dev)
+        vs = torch.ones(kvh, device=dev)
+    q = torch.randn(batch, h, 128, generator=g).bfloat16()
+    ar = torch.arange(hi, device=dev)
+    onehot_full = torch.zeros(hi, 128, dtype=torch.bfloat16, device=dev)
+    onehot_full[ar, ar % 128] = 1
+    zeros = [torch.zeros(n, kvh, 128, dtype=torch.bfloat16, device=dev) for n in lens]
+    onehot = [onehot_full[:n, None, :].expand(n, kvh, 128).contiguous() for n in lens]
+    kv = G.GpuKV(zeros, onehot, kvh, fp8=fp8, k_scale=ks, v_scale=vs)
+    try:
+        out = kv.attend(q, SCALE).float()
+        for i, n in enumerate(lens):
+            want = torch.bincount(torch.arange(n) % 128, minlength=128).float() / n
+            assert (out[i] - want[None, :]).abs().max() <= 2e-3, (name, i, n)
+    finally:
+        kv.close()
+    del zeros, onehot
+    rk = [torch.randn(n, kvh, 128, device=dev, dtype=torch.bfloat16) for n in lens]
+    ones = [torch.ones(n, kvh, 128, dtype=torch.bfloat16, device=dev) for n in lens]
+    if fp8:
+        ks = torch.full((kvh,), 6.0 / 448.0, device=dev)
+    kv = G.GpuKV(rk, ones, kvh, fp8=fp8, k_scale=ks, v_scale=vs)
+    try:
+        out = kv.attend(q, SCALE).float()
+        assert (out - 1).abs().max() <= 2e-3, name
+    finally:
+        kv.close()
+
+
 def test_empty_batch_and_zero_length(G):
     from glake_b200 import ops
     q = torch.zeros(0, 8, 128, dtype=torch.bfloat16, device="cuda")
