@@ -14,7 +14,7 @@ VT_OK = 0
 VT_ERR_INVALID, VT_ERR_DRIVER, VT_ERR_POOL_EMPTY, VT_ERR_RESERVE, VT_ERR_TIMEOUT = 1, 2, 3, 4, 5
 VT_ERR_UNSUPPORTED, VT_ERR_CUDA, VT_ERR_STATE, VT_ERR_NO_DRIVER, VT_ERR_KERNEL = 6, 7, 8, 9, 10
 VT_ERR_TOO_LARGE = 11
-VT_STATIC_SCRATCH_BYTES = 12 << 20
+VT_STATIC_SCRATCH_BYTES = 16 << 20
 VT_STEP_OVERLAP = 1
 VT_KV_BF16, VT_KV_FP8_E4M3 = 0, 1
 

@@ -78,19 +78,6 @@ static void carve_flat(void *ws, int batch, int kvh, AttnParams *p) {
   p->fl_part = reinterpret_cast<float *>(c + kStatusBytes + flat_counter_bytes(batch, kvh));
 }
 
-// Two resident CTAs per SM of the current device.
-static int flat_grid() {
-  static int cached[64] = {0};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 2 * 148;
-  if (cached[dev] == 0) {
-    int sms = 0;
-    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
-    cached[dev] = std::min(2 * sms, kFlatMaxCtas);
-  }
-  return cached[dev];
-}
-
 int plan_attn(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits, AttnPlan *plan) {
   const int g = h / kvh;
   // Tensor-core engine wherever it applies (bf16 KV) — on the flat persistent
@@ -217,7 +204,6 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
       p.new_key_stride = new_key_stride; p.new_value_stride = new_value_stride; p.byte_off = byte_off;
     }
     vt::carve_flat(workspace, batch, kvh, &p);
-    p.n_ctas = vt::flat_grid();
 #ifdef VT_TRACE
     p.trace = getenv("VT_TRACE_PTR") ? reinterpret_cast<unsigned long long *>(strtoull(getenv("VT_TRACE_PTR"), nullptr, 0)) : nullptr;
 #endif

@@ -67,7 +67,7 @@ struct AttnParams {
 
 constexpr int kFlatMaxBatch = 1024;   // prefix table of the flat schedule lives in shared memory
 constexpr int kFlatPartRow = 132;     // floats per published piece state row (16-byte aligned)
-constexpr int kFlatMaxCtas = 320;     // 2 per SM on up to 160 SMs
+constexpr int kFlatMaxCtas = 444;     // 3 per SM on the 148 SMs of a B200 (a larger part just gets fewer per SM)
 
 struct PrefillParams {
   void *out; int64_t out_stride;      // bf16 [tokens, h, 128]; stride of a token row in elements

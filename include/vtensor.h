@@ -303,7 +303,7 @@ int vt_prefill_attn(void *out, int64_t out_stride, const void *q, int64_t q_stri
  *     contents (the ticket counters are cleared on every call).  Two calls that
  *     overlap on the GPU (different streams) race on it: serialise them;
  *   - the kernel status word of this buffer cannot be read back. */
-#define VT_STATIC_SCRATCH_BYTES (12u << 20)
+#define VT_STATIC_SCRATCH_BYTES (16u << 20)
 int vt_decode_attn_static(void *out, int64_t out_stride, const void *q, int64_t q_stride,
                           const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
                           const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len,
