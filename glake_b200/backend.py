@@ -220,7 +220,9 @@ class DecodeRunner:
             self.ev_in = [torch.cuda.Event() for _ in range(layers)]
             self.ev_out = [torch.cuda.Event() for _ in range(layers)]
             per_layer = batch * (hd + 2 * kd) * 2
-            self.io_group = max(1, min(layers, -(-(1 << 20) // per_layer)))   # >= 1 MiB per host->device copy
+            # >= 1 MiB per host->device copy and >= 4 layers per group: every group boundary is a
+            # cross-stream dependency that interrupts the layer-to-layer overlap of the kernels
+            self.io_group = max(1, min(layers, max(4, -(-(1 << 20) // per_layer))))
 
     def _body(self, meta):
         """Everything the device does in one step after the per-step integers have
