@@ -535,6 +535,61 @@ def test_full_size_properties_of_the_bench_shapes(G, name, batch, h, kvh, lo, hi
         kv.close()
 
 
+def test_slot_lifecycle_on_the_real_driver(G):
+    """release_seq keeps the pre-cached prefix of a slot mapped (and its bytes
+    intact), preempt_seq unmaps everything, chunks return to the pool, base
+    addresses survive, and a reused slot serves a new sequence correctly."""
+    from glake_b200 import ops, vmmAllocator as A
+    from glake_b200.backend import VTensorMetadata, prepare_step, VTensorCacheEngine
+    kvh, row = 8, 8 * 128 * 2                      # 2 KiB rows, 1024 rows per chunk
+    free0 = A.showFreeBlocks()
+    eng = VTensorCacheEngine(2, kvh, 128, 2, 8192, cache_seqs=1, cache_tokens=1)   # slot 0 pre-cached with 1 chunk
+    try:
+        seg0, seg1 = eng.vmm_kvcache_segment
+        assert seg0.actual_size == 2 << 20 and seg1.actual_size == 0
+        assert A.showFreeBlocks() == free0 - 4                                       # 2 layers x (K + V)
+        bases = [seg0.getKeyDevicePtr(1), seg1.getValueDevicePtr(0)]
+        rs = np.random.RandomState(2)
+        lens = [3000, 1500]
+        k = [synth.normal_bf16(rs, n, kvh, 128) for n in lens]
+        v = [synth.normal_bf16(rs, n, kvh, 128) for n in lens]
+        meta = VTensorMetadata([0, 1], lens, kvh, 128, num_prefills=2)
+        prepare_step(meta, eng)
+        for layer in range(2):
+            ops.reshape_and_cache(torch.cat(k).cuda(), torch.cat(v).cuda(), eng.k_cache_ptr[layer], eng.v_cache_ptr[layer],
+                                  meta.slot_m, meta.slot_mapping, meta.seq_lens_tensor, meta.cache_seq_lens, max(lens),
+                                  kvh, 128)
+        torch.cuda.synchronize()
+        assert seg0.actual_size == 6 << 20 and seg1.actual_size == 4 << 20          # 3 and 2 chunks per range
+        assert A.showFreeBlocks() == free0 - 4 * (3 + 2)
+        seg0.release_seq(0)                          # finished: keeps its 1-chunk prefix
+        seg1.preempt_seq(1)                          # preempted: everything goes back
+        assert (seg0.actual_size, seg0.used_size, seg1.actual_size) == (2 << 20, 0, 0)
+        assert A.showFreeBlocks() == free0 - 4
+        assert [seg0.getKeyDevicePtr(1), seg1.getValueDevicePtr(0)] == bases
+        holder = G.GpuKV.__new__(G.GpuKV)
+        holder.engine, holder.kvh, holder.fp8, holder.layer, holder.slots, holder.lens = eng, kvh, False, 1, [0, 1], [1024, 0]
+        assert torch.equal(holder.read_rows(0, "k"), k[0][:1024])      # the kept chunk still holds the old rows
+        # both slots serve new sequences
+        lens2 = [700, 2100]
+        q, k2, v2 = synth.make_case(91, lens2, 16, kvh)
+        meta = VTensorMetadata([0, 1], lens2, kvh, 128, num_prefills=2)
+        prepare_step(meta, eng)
+        ops.reshape_and_cache(torch.cat(k2).cuda(), torch.cat(v2).cuda(), eng.k_cache_ptr[0], eng.v_cache_ptr[0],
+                              meta.slot_m, meta.slot_mapping, meta.seq_lens_tensor, meta.cache_seq_lens, max(lens2), kvh, 128)
+        out = torch.empty(2, 16, 128, dtype=torch.bfloat16, device="cuda")
+        ops.paged_attention_v1(out, q.cuda(), eng.gpu_cache[0][0].vmm_ptr, eng.gpu_cache[0][1].vmm_ptr, kvh, SCALE,
+                               meta.seq_lens_tensor, 1, max(lens2), None, "auto", 1.0, meta.slot_mapping)
+        from oracle import oracle as O
+        r = O.fill_ranges(k2, v2)
+        port = O.port_decode_attn(q, r, torch.arange(2), torch.tensor(lens2, dtype=torch.int32), kvh, SCALE)
+        ok, err = close_2e3(out.cpu(), port, ulp_slack=True)
+        assert ok, err
+    finally:
+        eng.close()
+    assert A.showFreeBlocks() == free0
+
+
 def test_empty_batch_and_zero_length(G):
     from glake_b200 import ops
     q = torch.zeros(0, 8, 128, dtype=torch.bfloat16, device="cuda")
