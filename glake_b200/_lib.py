@@ -76,6 +76,10 @@ def _load():
         "vt_append": (c_int, [vp, vp, c_int64, c_int64, vp, vp, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                               vp, vp, vp]),
         "vt_kv_scales": (c_int, [vp, c_int64, c_int, c_int, c_int, vp, vp]),
+        "vt_rope_append": (c_int, [vp, vp, c_int64, c_int, vp, vp, c_int64, c_int64, vp, c_int, c_int, vp, vp, vp, vp,
+                                   vp, vp, c_int, c_int, c_int, c_int, c_int, vp, vp, ctypes.c_uint, vp]),
+        "vt_rms_norm": (c_int, [vp, vp, vp, c_float, c_int, c_int, c_int64, c_int64, vp]),
+        "vt_fused_add_rms_norm": (c_int, [vp, vp, vp, c_float, c_int, c_int, vp]),
         "vt_decode_attn_workspace_bytes": (c_int, [c_int, c_int, c_int, c_int, POINTER(sz)]),
         "vt_decode_attn": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                                    c_float, c_int, vp, vp, vp, vp, sz, c_int, vp]),

@@ -83,6 +83,65 @@ def reshape_and_cache(key, value, key_cache, value_cache, slot_m, slot_mapping, 
                             _kv_dtype(kv_cache_dtype), _ptr(k_scale), _ptr(v_scale), _stream()), "vt_append")
 
 
+VT_ROPE_WRITE_KEY = 1
+
+
+def rotary_embedding_and_cache(positions, query, key, value, head_size, cos_sin_cache, is_neox, key_cache,
+                               value_cache, slot_m, slot_mapping, seq_lens, cache_seq_lens, max_seq_len,
+                               num_kv_heads, kv_cache_dtype="auto", k_scale=None, v_scale=None, write_key=False):
+    """``rotary_embedding`` (GLakeServe/vllm/_custom_ops.py:81-90) and
+    ``reshape_and_cache`` in one launch: ``query`` is rotated in place, the rotated
+    key and the value rows go straight into the slots' ranges.  The first seven
+    arguments are rotary_embedding's (plus ``value``), the rest reshape_and_cache's.
+    ``key`` itself is only rewritten with ``write_key=True``."""
+    _require_cuda(positions, query, key, value, cos_sin_cache, key_cache, value_cache, slot_m, slot_mapping)
+    if not (query.dtype == key.dtype == value.dtype == cos_sin_cache.dtype == torch.bfloat16):
+        raise RuntimeError("rotary_embedding_and_cache: bfloat16 tensors only")
+    q2 = query.view(-1, query.shape[-1])
+    k2 = key.view(-1, key.shape[-1])
+    v2 = value.view(-1, value.shape[-1])
+    if q2.stride(1) != 1 or k2.stride(1) != 1 or v2.stride(1) != 1 or not cos_sin_cache.is_contiguous():
+        raise RuntimeError("rotary_embedding_and_cache: rows must be contiguous")
+    if q2.shape[-1] % head_size or k2.shape[-1] != num_kv_heads * head_size or v2.shape[-1] != k2.shape[-1]:
+        raise RuntimeError("rotary_embedding_and_cache: inconsistent head counts")
+    with torch.cuda.device(query.device):
+        check(lib.vt_rope_append(_ptr(positions), _ptr(q2), q2.stride(0), q2.shape[-1] // head_size, _ptr(k2), _ptr(v2),
+                                 k2.stride(0), v2.stride(0), _ptr(cos_sin_cache), cos_sin_cache.shape[1],
+                                 1 if is_neox else 0, _ptr(key_cache), _ptr(value_cache), _ptr(slot_m),
+                                 _ptr(slot_mapping), _ptr(seq_lens), _ptr(cache_seq_lens), int(max_seq_len),
+                                 slot_mapping.numel(), num_kv_heads, head_size, _kv_dtype(kv_cache_dtype),
+                                 _ptr(k_scale), _ptr(v_scale), VT_ROPE_WRITE_KEY if write_key else 0, _stream()),
+              "vt_rope_append")
+
+
+def rms_norm(out, input, weight, epsilon):
+    """out = rms_norm(input) * weight (GLakeServe/vllm/_custom_ops.py:104-106)."""
+    _require_cuda(out, input, weight)
+    if not (out.dtype == input.dtype == weight.dtype == torch.bfloat16):
+        raise RuntimeError("rms_norm: bfloat16 tensors only")
+    hidden = input.shape[-1]
+    x, o = input.view(-1, hidden), out.view(-1, hidden)
+    if x.stride(1) != 1 or o.stride(1) != 1:
+        raise RuntimeError("rms_norm: rows must be contiguous")
+    with torch.cuda.device(input.device):
+        check(lib.vt_rms_norm(_ptr(o), _ptr(x), _ptr(weight), float(epsilon), x.shape[0], hidden, x.stride(0),
+                              o.stride(0), _stream()), "vt_rms_norm")
+
+
+def fused_add_rms_norm(input, residual, weight, epsilon):
+    """residual += input; input = rms_norm(residual) * weight, both in place
+    (GLakeServe/vllm/_custom_ops.py:109-111)."""
+    _require_cuda(input, residual, weight)
+    if not (input.dtype == residual.dtype == weight.dtype == torch.bfloat16):
+        raise RuntimeError("fused_add_rms_norm: bfloat16 tensors only")
+    if not (input.is_contiguous() and residual.is_contiguous()):
+        raise RuntimeError("fused_add_rms_norm: contiguous tensors only")
+    hidden = input.shape[-1]
+    with torch.cuda.device(input.device):
+        check(lib.vt_fused_add_rms_norm(_ptr(input), _ptr(residual), _ptr(weight), float(epsilon),
+                                        input.numel() // hidden, hidden, _stream()), "vt_fused_add_rms_norm")
+
+
 def kv_scales(x, num_kv_heads, head_size):
     """Per-kv-head scale = amax / 448 of x ([tokens, kv_heads, head_size] bf16)."""
     _require_cuda(x)

@@ -276,6 +276,52 @@ int vt_prefill_attn(void *out, int64_t out_stride, const void *q, int64_t q_stri
                     const int32_t *q_lens, const int32_t *q_start, int batch, int h, int kvh, int d,
                     int max_q_len, float scale, int kv_dtype, uint32_t *status, void *stream);
 
+/* ---- element-wise steps either side of the attention --------------------- */
+/* Rotary embedding of q and k followed by the KV append, in one launch.
+ * Replaces the pair rotary_embedding (csrc/pos_encoding_kernels.cu:77-130,
+ * declared csrc/ops.h:52-58; called at vllm/model_executor/models/llama.py:172-181)
+ * + reshape_and_cache (csrc/cache_kernels.cu:153-200): the rotated key goes
+ * straight into the slot's range instead of making a round trip through memory.
+ *   positions      device int64 [tokens]: position of each token row
+ *   query          bf16 [tokens, num_heads, d], rotated IN PLACE; stride of dim 0 in elements
+ *   key, value     bf16 [tokens, kvh, d]; key is left untouched unless
+ *                  VT_ROPE_WRITE_KEY is given (the reference's rotary_embedding
+ *                  rotates it in place; only callers that read key again need that)
+ *   cos_sin_cache  bf16 [max_position, rot_dim]: cos of the rot_dim/2 frequencies,
+ *                  then their sin (vllm/model_executor/layers/rotary_embedding.py:83-93)
+ *   rot_dim        multiple of 16, <= d; elements beyond it pass through unrotated
+ *   is_neox        non-zero: pairs (j, j + rot_dim/2); zero: GPT-J pairs (2j, 2j+1)
+ *   the remaining arguments are vt_append's, with the same meaning; token row
+ *   numbering (decode: row i; prefill: cache_seq_lens[i] + t) also indexes positions.
+ * Arithmetic as the reference's CPU kernel (csrc/cpu/pos_encoding.cpp:23-89,
+ * :109-166): fp32 products, one rounding to bf16; with an fp8 cache the rounded
+ * bf16 key is what gets quantised, as in the two-kernel sequence.  Pointers must
+ * be 16-byte aligned and strides multiples of 8 elements (VT_ERR_UNSUPPORTED). */
+#define VT_ROPE_WRITE_KEY 1u
+int vt_rope_append(const int64_t *positions, void *query, int64_t query_stride, int num_heads, void *key,
+                   const void *value, int64_t key_stride, int64_t value_stride, const void *cos_sin_cache,
+                   int rot_dim, int is_neox, const uint64_t *k_table, const uint64_t *v_table,
+                   const int64_t *byte_off, const int64_t *slot_ids, const int32_t *seq_lens,
+                   const int32_t *cache_seq_lens, int max_seq_len, int batch, int kvh, int d, int kv_dtype,
+                   const float *k_scale, const float *v_scale, unsigned flags, void *stream);
+
+/* out = input * rsqrt(mean(input^2) + epsilon) * weight per token row.
+ * Replaces rms_norm (csrc/layernorm_kernels.cu:21-47, :277-297; csrc/ops.h:40-44).
+ *   out, input   bf16 [num_tokens, hidden]; row strides in elements (out may alias input)
+ *   weight       bf16 [hidden]
+ * hidden must be a multiple of 8 and at most 16384; 16-byte aligned pointers. */
+int vt_rms_norm(void *out, const void *input, const void *weight, float epsilon, int num_tokens, int hidden,
+                int64_t input_stride, int64_t out_stride, void *stream);
+
+/* residual += input (stored back to residual), then input = rms_norm(residual) * weight,
+ * both contiguous bf16 [num_tokens, hidden].  Replaces fused_add_rms_norm
+ * (csrc/layernorm_kernels.cu:187-274, :318-352; csrc/ops.h:46-50), the op on either
+ * side of the attention block (vllm/model_executor/models/llama.py:245-259).
+ * Arithmetic as csrc/cpu/layernorm.cpp:44-88: the variance is taken from the
+ * fp32 sums, the scaling from the sums after their rounding to bf16. */
+int vt_fused_add_rms_norm(void *input, void *residual, const void *weight, float epsilon, int num_tokens,
+                          int hidden, void *stream);
+
 /* vt_decode_attn for callers that cannot allocate device memory at all.
  * (No counterpart in the reference: its attention ops get their scratch from
  * torch's allocator.)

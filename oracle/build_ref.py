@@ -1,7 +1,7 @@
 """TEST INFRASTRUCTURE — builds the reference's own CPU kernels as a checker.
 
-Compiles GLakeServe/csrc/cpu/attention.cpp and cache.cpp (unmodified, read from
-the reference checkout) together with oracle/ref_shim.cpp into a Python
+Compiles GLakeServe/csrc/cpu/attention.cpp, cache.cpp, pos_encoding.cpp and
+layernorm.cpp (unmodified, read from the reference checkout) together with oracle/ref_shim.cpp into a Python
 extension under oracle/_ref/.  Two variants are produced because the machine
 that later loads the prebuilt file may lack the AVX512-BF16 extension:
 
@@ -33,7 +33,9 @@ def build(reference_root, verbose=False):
     cpu_dir = os.path.join(reference_root, "GLakeServe", "csrc", "cpu")
     srcs = [os.path.join(HERE, "ref_shim.cpp"),
             os.path.join(cpu_dir, "attention.cpp"),
-            os.path.join(cpu_dir, "cache.cpp")]
+            os.path.join(cpu_dir, "cache.cpp"),
+            os.path.join(cpu_dir, "pos_encoding.cpp"),
+            os.path.join(cpu_dir, "layernorm.cpp")]
     for s in srcs:
         if not os.path.isfile(s):
             raise FileNotFoundError(s)

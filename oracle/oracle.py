@@ -168,6 +168,35 @@ def port_prefill_attn(q, ranges, slot_ids, seq_lens, q_lens, q_start, kvh, scale
     return out
 
 
+def port_rotary_embedding(positions, query, key, head_size, cos_sin_cache, is_neox=True):
+    """Rotates query [T, H*D] and key [T, KVH*D] (bf16, dim-0 stride free) in place."""
+    lib = load_port()
+    lib.vto_rotary_embedding(_p(positions), _p(query), _p(key), _p(cos_sin_cache),
+                             ctypes.c_int(cos_sin_cache.shape[1]), c_i64(query.stride(0)),
+                             c_i64(key.stride(0)), ctypes.c_int(query.shape[-1] // head_size),
+                             ctypes.c_int(key.shape[-1] // head_size), ctypes.c_int(head_size),
+                             ctypes.c_int(query.shape[0]), ctypes.c_int(1 if is_neox else 0))
+
+
+def port_rms_norm(out, input, weight, epsilon, residual=None):
+    """out = rms_norm(input [+ residual, stored back]) * weight; contiguous bf16 [T, hidden]."""
+    lib = load_port()
+    lib.vto_rms_norm(_p(out), _p(input), _p(residual), _p(weight), c_f32(epsilon),
+                     ctypes.c_int(input.shape[0]), ctypes.c_int(input.shape[1]))
+
+
+def make_cos_sin_cache(max_position, rot_dim, base=10000.0):
+    """The table RotaryEmbedding builds
+    (GLakeServe/vllm/model_executor/layers/rotary_embedding.py:71-93), in bf16.
+    Evaluated in float64 so that the bf16 table does not depend on which
+    vectorised cos/sin the host's math library picks."""
+    import numpy as np
+    inv_freq = 1.0 / (base ** (np.arange(0, rot_dim, 2, dtype=np.float64) / rot_dim))
+    freqs = np.outer(np.arange(max_position, dtype=np.float64), inv_freq)
+    table = np.concatenate((np.cos(freqs), np.sin(freqs)), axis=-1).astype(np.float32)
+    return torch.from_numpy(table).to(torch.bfloat16)
+
+
 def fill_ranges(k_list, v_list, range_bytes=None, k_scale=None, v_scale=None):
     """Build HostRanges holding the given per-sequence K/V ([L_i, KVH, D] bf16)
     by appending every row through the port's append (slot i = sequence i)."""

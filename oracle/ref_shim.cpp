@@ -3,9 +3,11 @@
 // Binding shim for the reference's CPU-backend kernels. The reference's own
 // csrc/cpu/pybind.cpp does not compile (it includes the CUDA-side headers whose
 // signatures differ from the CPU definitions), so this translation unit
-// forward-declares the three entry points with the signatures their CPU
+// forward-declares the entry points with the signatures their CPU
 // definitions actually have (GLakeServe/csrc/cpu/attention.cpp:415-422 and
-// :730-738, GLakeServe/csrc/cpu/cache.cpp:103-106) and exposes them to Python.
+// :730-738, GLakeServe/csrc/cpu/cache.cpp:103-106,
+// GLakeServe/csrc/cpu/pos_encoding.cpp:169-171,
+// GLakeServe/csrc/cpu/layernorm.cpp:90-91, :104-105) and exposes them to Python.
 // The reference sources themselves are compiled unmodified, from where they
 // lie, by oracle/build_ref.py.
 #include <torch/extension.h>
@@ -33,8 +35,21 @@ void reshape_and_cache(torch::Tensor &key, torch::Tensor &value,
                        torch::Tensor &slot_mapping,
                        const std::string &kv_cache_dtype, float kv_scale);
 
+void rotary_embedding(torch::Tensor &positions, torch::Tensor &query,
+                      torch::Tensor &key, int head_size,
+                      torch::Tensor &cos_sin_cache, bool is_neox);
+
+void rms_norm(torch::Tensor &out, torch::Tensor &input, torch::Tensor &weight,
+              float epsilon);
+
+void fused_add_rms_norm(torch::Tensor &input, torch::Tensor &residual,
+                        torch::Tensor &weight, float epsilon);
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_attention_v1", &paged_attention_v1);
   m.def("paged_attention_v2", &paged_attention_v2);
   m.def("reshape_and_cache", &reshape_and_cache);
+  m.def("rotary_embedding", &rotary_embedding);
+  m.def("rms_norm", &rms_norm);
+  m.def("fused_add_rms_norm", &fused_add_rms_norm);
 }

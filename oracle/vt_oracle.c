@@ -23,6 +23,12 @@
  *   - prefill:          GLakeServe/csrc/cache_kernels.cu:168-190 (multi-token
  *                       append) and the causal prefix attention the backend
  *                       requests at GLakeServe/vllm/attention/backends/xformers.py:362-385.
+ *   - rotary embedding: GLakeServe/csrc/cpu/pos_encoding.cpp:23-89 (NeoX pairs
+ *                       (j, j + rot/2)) and :109-166 (GPT-J pairs (2j, 2j+1)):
+ *                       fp32 products, one rounding to bf16, q and k in place.
+ *   - rms norm:         GLakeServe/csrc/cpu/layernorm.cpp:5-41 and :44-88
+ *                       (fused residual add: variance from the fp32 sums, scaling
+ *                       from the sums after rounding to bf16).
  *
  * Parity pin: tests/test_oracle.py checks this file against the reference's
  * own CPU kernels compiled by oracle/build_ref.py, and against the golden
@@ -275,5 +281,61 @@ void vto_prefill_attn(bf16_t *out, int64_t out_stride, const bf16_t *q,
       }
     }
     free(logits);
+  }
+}
+
+/* Rotary embedding of q and k in place (pos_encoding.cpp:23-89, :109-166).
+ * cos_sin: bf16 [max_position, rot_dim], cos of the rot_dim/2 frequencies then sin. */
+void vto_rotary_embedding(const int64_t *positions, bf16_t *query, bf16_t *key,
+                          const bf16_t *cos_sin, int rot_dim, int64_t query_stride,
+                          int64_t key_stride, int num_heads, int num_kv_heads,
+                          int head_size, int num_tokens, int is_neox) {
+  const int half = rot_dim / 2;
+#pragma omp parallel for
+  for (int t = 0; t < num_tokens; ++t) {
+    const bf16_t *cs = cos_sin + positions[t] * rot_dim;
+    for (int pass = 0; pass < 2; ++pass) {
+      bf16_t *base = pass == 0 ? query + t * query_stride : key + t * key_stride;
+      const int heads = pass == 0 ? num_heads : num_kv_heads;
+      for (int h = 0; h < heads; ++h) {
+        bf16_t *v = base + (int64_t)h * head_size;
+        for (int j = 0; j < half; ++j) {
+          const int xi = is_neox ? j : 2 * j, yi = is_neox ? half + j : 2 * j + 1;
+          const float c = bf16_to_f32(cs[j]), s = bf16_to_f32(cs[half + j]);
+          const float x = bf16_to_f32(v[xi]), y = bf16_to_f32(v[yi]);
+          v[xi] = f32_to_bf16(fmaf(x, c, -(y * s)));
+          v[yi] = f32_to_bf16(fmaf(y, c, x * s));
+        }
+      }
+    }
+  }
+}
+
+/* out = x * (1 / sqrt(mean(x^2) + eps)) * w; with residual != NULL first
+ * x = input + residual (fp32), residual = bf16(x), and the scaling uses the
+ * rounded value while the variance uses the fp32 one (layernorm.cpp:5-41, :44-88). */
+void vto_rms_norm(bf16_t *out, const bf16_t *input, bf16_t *residual, const bf16_t *weight,
+                  float eps, int num_tokens, int hidden) {
+#pragma omp parallel for
+  for (int t = 0; t < num_tokens; ++t) {
+    const bf16_t *in = input + (int64_t)t * hidden;
+    bf16_t *res = residual ? residual + (int64_t)t * hidden : NULL;
+    bf16_t *o = out + (int64_t)t * hidden;
+    float lanes[8] = {0};
+    for (int j = 0; j < hidden; ++j) {
+      float x = bf16_to_f32(in[j]);
+      if (res) {
+        x += bf16_to_f32(res[j]);
+        res[j] = f32_to_bf16(x);
+      }
+      lanes[j & 7] = fmaf(x, x, lanes[j & 7]);
+    }
+    float ss = 0.f;
+    for (int l = 0; l < 8; ++l) ss += lanes[l];
+    const float s = 1.0f / sqrtf(ss / (float)hidden + eps);
+    for (int j = 0; j < hidden; ++j) {
+      const float x = bf16_to_f32(res ? res[j] : in[j]);
+      o[j] = f32_to_bf16(x * s * bf16_to_f32(weight[j]));
+    }
   }
 }

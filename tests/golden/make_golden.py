@@ -10,6 +10,11 @@ call, then paged_attention_v1 / _v2 (GLakeServe/csrc/cpu/attention.cpp:415-430,
 (uint16 view of bf16), context lengths, a sha256 of the inputs, and a sha256 of
 the cache contents gathered back to [token, kv_head, d] order.
 
+tests/synth.py:ROPE_CASES and NORM_CASES go through the reference's CPU
+rotary_embedding (GLakeServe/csrc/cpu/pos_encoding.cpp:169-198) and rms_norm /
+fused_add_rms_norm (GLakeServe/csrc/cpu/layernorm.cpp:90-117); the rotated q / k
+and the normalised rows are stored as bf16 bit patterns.
+
 Usage: python tests/golden/make_golden.py
 """
 import os
@@ -58,6 +63,40 @@ def run_case(name):
     print(name, "lens", lens[:8], "out", tuple(out.shape), "max|out|", float(out.float().abs().max()))
 
 
+def bits(t):
+    return t.contiguous().view(torch.uint16).numpy()
+
+
+def run_rope_case(name):
+    seed, tokens, h, kvh, rot, neox, max_pos = synth.ROPE_CASES[name]
+    ref = O.load_ref("bf16")
+    pos, q, k, v = synth.make_rope_case(seed, tokens, h, kvh, max_pos)
+    cs = O.make_cos_sin_cache(max_pos, rot)
+    sha = synth.digest(pos, q, k, v, cs)
+    ref.rotary_embedding(pos, q, k, 128, cs, neox)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), q_bits=bits(q), k_bits=bits(k),
+                        input_sha256=np.asarray(sha))
+    print(name, "q", tuple(q.shape), "k", tuple(k.shape))
+
+
+def run_norm_case(name):
+    seed, tokens, hidden, eps = synth.NORM_CASES[name]
+    ref = O.load_ref("bf16")
+    x, r, w = synth.make_norm_case(seed, tokens, hidden)
+    sha = synth.digest(x, r, w)
+    plain = torch.empty_like(x)
+    ref.rms_norm(plain, x, w, eps)
+    fx, fr = x.clone(), r.clone()
+    ref.fused_add_rms_norm(fx, fr, w, eps)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), plain_bits=bits(plain), fused_bits=bits(fx),
+                        residual_bits=bits(fr), input_sha256=np.asarray(sha))
+    print(name, tuple(x.shape))
+
+
 if __name__ == "__main__":
     for name in synth.GOLDEN_CASES:
         run_case(name)
+    for name in synth.ROPE_CASES:
+        run_rope_case(name)
+    for name in synth.NORM_CASES:
+        run_norm_case(name)

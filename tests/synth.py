@@ -53,3 +53,30 @@ def golden_lens(name):
     if isinstance(lens, tuple):
         lens = uniform_lens(seed, *lens[1:])
     return seed, lens, h, kvh
+
+
+# name -> (seed, tokens, H, KVH, rot_dim, is_neox, max_position)
+ROPE_CASES = {
+    "rope_neox": (11, 12, 4, 2, 128, True, 4096),
+    "rope_gptj_partial": (12, 9, 4, 1, 64, False, 2048),
+}
+# name -> (seed, tokens, hidden, epsilon)
+NORM_CASES = {
+    "norm_1024": (21, 6, 1024, 1e-5),
+    "norm_4096": (22, 3, 4096, 1e-6),
+}
+
+
+def make_rope_case(seed, tokens, h, kvh, max_position, d=128):
+    """positions int64 [T]; q [T, H*D]; k, v [T, KVH*D] ~N(0,1) bf16."""
+    rs = np.random.RandomState(seed)
+    pos = torch.from_numpy(rs.randint(0, max_position, size=tokens).astype(np.int64))
+    return pos, normal_bf16(rs, tokens, h * d), normal_bf16(rs, tokens, kvh * d), normal_bf16(rs, tokens, kvh * d)
+
+
+def make_norm_case(seed, tokens, hidden):
+    """x, residual [T, hidden] ~N(0,1); weight [hidden] ~ 1 + 0.1 N(0,1); bf16."""
+    rs = np.random.RandomState(seed)
+    x, r = normal_bf16(rs, tokens, hidden), normal_bf16(rs, tokens, hidden)
+    w = torch.from_numpy((1.0 + 0.1 * rs.standard_normal(hidden)).astype(np.float32)).bfloat16()
+    return x, r, w

@@ -162,3 +162,62 @@ def test_prefill_attention_is_causal(oracle):
             n = lens[i] - int(q_lens[i]) + j + 1
             want = oracle.torch_decode_attn(qq[int(q_start[i]) + j][None], [k[i][:n]], [v[i][:n]], SCALE)[0]
             assert one_ulp_close(out[int(q_start[i]) + j], want.bfloat16(), 1e-5)
+
+
+def _from_bits(a):
+    return torch.from_numpy(a.copy()).view(torch.bfloat16)
+
+
+@pytest.mark.parametrize("name", list(synth.ROPE_CASES))
+def test_port_rotary_matches_golden(oracle, name):
+    """The restated rotary embedding reproduces the reference CPU kernel's q and k bit for bit."""
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    seed, tokens, h, kvh, rot, neox, max_pos = synth.ROPE_CASES[name]
+    pos, q, k, v = synth.make_rope_case(seed, tokens, h, kvh, max_pos)
+    cs = oracle.make_cos_sin_cache(max_pos, rot)
+    assert synth.digest(pos, q, k, v, cs) == str(z["input_sha256"]), "input generator drifted"
+    q0 = q.clone()
+    oracle.port_rotary_embedding(pos, q, k, 128, cs, neox)
+    assert torch.equal(q, _from_bits(z["q_bits"])) and torch.equal(k, _from_bits(z["k_bits"]))
+    if rot < 128:   # elements beyond rot_dim pass through
+        assert torch.equal(q.view(tokens, h, 128)[..., rot:], q0.view(tokens, h, 128)[..., rot:])
+
+
+@pytest.mark.parametrize("name", list(synth.NORM_CASES))
+def test_port_rms_norm_matches_golden(oracle, name):
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    seed, tokens, hidden, eps = synth.NORM_CASES[name]
+    x, r, w = synth.make_norm_case(seed, tokens, hidden)
+    assert synth.digest(x, r, w) == str(z["input_sha256"]), "input generator drifted"
+    plain = torch.empty_like(x)
+    oracle.port_rms_norm(plain, x, w, eps)
+    fx, fr = x.clone(), r.clone()
+    oracle.port_rms_norm(fx, fx, w, eps, residual=fr)
+    assert torch.equal(fr, _from_bits(z["residual_bits"]))          # one fp32 add, one rounding: exact
+    # the sum of squares may be taken in another order: at most one bf16 rounding flip
+    assert one_ulp_close(plain, _from_bits(z["plain_bits"]), 0.0)
+    assert one_ulp_close(fx, _from_bits(z["fused_bits"]), 0.0)
+    assert (plain == _from_bits(z["plain_bits"])).float().mean() > 0.99
+
+
+def test_port_rotary_and_norm_match_live_reference(oracle):
+    ref = oracle.load_ref()
+    if ref is None:
+        pytest.skip("prebuilt reference CPU kernels do not load on this CPU")
+    exact = oracle._cpu_has("avx512_bf16")      # the plain AVX-512 build truncates instead of rounding
+    pos, q, k, v = synth.make_rope_case(5, 33, 8, 8, 8192)
+    for rot, neox in ((128, True), (128, False), (32, True)):
+        cs = oracle.make_cos_sin_cache(8192, rot)
+        q1, k1, q2, k2 = q.clone(), k.clone(), q.clone(), k.clone()
+        ref.rotary_embedding(pos, q1, k1, 128, cs, neox)
+        oracle.port_rotary_embedding(pos, q2, k2, 128, cs, neox)
+        if exact:
+            assert torch.equal(q1, q2) and torch.equal(k1, k2)
+        else:
+            assert one_ulp_close(q1, q2, 0.0) and one_ulp_close(k1, k2, 0.0)
+    x, r, w = synth.make_norm_case(6, 5, 8192)
+    a, b = x.clone(), x.clone()
+    ra, rb = r.clone(), r.clone()
+    ref.fused_add_rms_norm(a, ra, w, 1e-5)
+    oracle.port_rms_norm(b, b, w, 1e-5, residual=rb)
+    assert one_ulp_close(a, b, 0.0) and one_ulp_close(ra, rb, 0.0)
