@@ -1,0 +1,354 @@
+// Low-latency sum all-reduce of small bf16 messages over NVLink peer memory: the
+// model-level reduction after o_proj / down_proj of a tensor-parallel layer, for
+// messages too small for a bandwidth-optimised collective to get going.
+//
+// Every rank owns one buffer that all ranks have mapped (CUDA IPC or any other
+// peer mapping): two flag arrays, two staging copies of the message and two result
+// copies (double-buffered by call parity).  One kernel launch per call, the same
+// fixed grid on every rank; CTA b owns slice b of the message on every rank and
+// synchronises only with CTA b of the peers:
+//
+//   stage     in[slice b] -> own staging[parity]
+//   barrier A store the call number into flagsA[b][me] of every rank (release.sys),
+//             poll own flagsA[b][r] for every r (acquire.sys, local memory)
+//   one-shot  (small messages, or two ranks): out[v] = sum_r staging_r[v], rank order
+//   two-shot  reduce sub-slice `me` of slice b from all ranks' staging and PUSH the
+//             result into every rank's result copy; barrier B; copy own result -> out
+//
+// Accumulation is fp32 in rank order 0..world-1 with one rounding to bf16, so all
+// ranks hold bit-identical results (the rule of csrc/custom_all_reduce.cuh:173-181,
+// :196-197 in the reference).  Flags carry a monotonically increasing call number
+// kept per CTA in device memory: nothing is reset, a peer that runs one call ahead
+// cannot be misread (the test is flag - call >= 0), and the launch arguments never
+// change, so the call can sit inside a CUDA graph.  Why double buffering suffices:
+// CTA b reuses staging[parity] two calls later, after it passed barrier A of the
+// call in between, which every peer's CTA b signals only after it finished reading.
+//
+// Every wait is bounded by wall time (%globaltimer); when it runs out the CTA sets
+// the status word, keeps signalling so that nobody else waits for it, and returns.
+// Peer data moves with plain loads and stores only (no multimem, no TMA).
+#include "../../include/vtensor.h"
+#include "vt_device.cuh"
+
+#include <algorithm>
+#include <cstdint>
+#include <cstring>
+#include <new>
+
+namespace vt {
+namespace {
+
+constexpr int kArMaxWorld = 8;
+constexpr int kArMaxCtas = 64;
+constexpr int kArThreads = 512;
+constexpr size_t kArFlagBytes = 4096;                        // one flag array: [64 CTAs][8 ranks] u32 = 2 KiB, padded
+constexpr uint32_t kArTimedOut = 0xDEAD0A88u;
+
+struct ArDev {                                               // lives in local device memory
+  int rank, world, n_ctas, one_shot_vecs;
+  unsigned long long wait_ns;
+  size_t max_bytes;
+  char *peer[kArMaxWorld];                                   // shared buffer of every rank, as mapped here
+  uint32_t *epoch;                                           // [n_ctas] call numbers (local)
+  uint32_t *status;                                          // local
+};
+
+struct ArLaunch {                                            // index = blockIdx.y (0 unless ranks are emulated on one GPU)
+  ArDev dev[kArMaxWorld];                                    // by value: no dependent load before the first flag goes out
+  const void *in[kArMaxWorld];
+  void *out[kArMaxWorld];
+};
+
+__device__ __forceinline__ uint32_t *flags_a(char *buf) { return reinterpret_cast<uint32_t *>(buf); }
+__device__ __forceinline__ uint32_t *flags_b(char *buf) { return reinterpret_cast<uint32_t *>(buf + kArFlagBytes); }
+__device__ __forceinline__ uint4 *staging(char *buf, size_t max_bytes, int parity) {
+  return reinterpret_cast<uint4 *>(buf + 2 * kArFlagBytes + parity * max_bytes);
+}
+__device__ __forceinline__ uint4 *result(char *buf, size_t max_bytes, int parity) {
+  return reinterpret_cast<uint4 *>(buf + 2 * kArFlagBytes + (2 + parity) * max_bytes);
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys(const uint4 *p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+// Threads r < world: tell rank r that this CTA reached call `e`, then wait until rank r
+// said the same.  All threads return true unless some wait ran out of time.
+__device__ __forceinline__ bool cta_barrier(const ArDev &d, bool second, uint32_t e, int *timed_out) {
+  __syncthreads();                                           // every thread's earlier writes precede the release below
+  const int b = blockIdx.x, r = threadIdx.x;
+  if (r < d.world) {
+    uint32_t *theirs = (second ? flags_b(d.peer[r]) : flags_a(d.peer[r])) + b * kArMaxWorld + d.rank;
+    st_release_sys(theirs, e);
+    const uint32_t *mine = (second ? flags_b(d.peer[d.rank]) : flags_a(d.peer[d.rank])) + b * kArMaxWorld + r;
+    const unsigned long long t0 = global_ns();
+    for (unsigned it = 0;; ++it) {
+      if (static_cast<int>(ld_acquire_sys(mine) - e) >= 0) break;
+      if ((it & 63u) == 63u && global_ns() - t0 > d.wait_ns) {
+        *timed_out = 1;
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return *timed_out == 0;
+}
+
+__device__ __forceinline__ void add8(float *acc, const uint4 &v) {
+  acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
+  acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
+}
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+// Sums vectors [lo, hi) of all ranks' staging copies, U vectors of every rank in
+// flight per thread before the first add (a peer load is a ~2 us round trip), and
+// hands each sum to `sink(v, sum)`.
+template <int W, typename Sink>
+__device__ __forceinline__ void reduce_range(const ArDev &d, int parity, int lo, int hi, Sink sink) {
+  constexpr int U = W <= 2 ? 4 : (W <= 4 ? 2 : 1);
+  const uint4 *src[W];
+#pragma unroll
+  for (int r = 0; r < W; ++r) src[r] = staging(d.peer[r], d.max_bytes, parity);
+  for (int v0 = lo + threadIdx.x; v0 < hi; v0 += kArThreads * U) {
+    uint4 x[U][W];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * kArThreads;
+      if (v < hi) {
+#pragma unroll
+        for (int r = 0; r < W; ++r) x[u][r] = ld_relaxed_sys(src[r] + v);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * kArThreads;
+      if (v < hi) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int r = 0; r < W; ++r) add8(acc, x[u][r]);
+        sink(v, make_uint4(pack2(acc[0], acc[1]), pack2(acc[2], acc[3]), pack2(acc[4], acc[5]), pack2(acc[6], acc[7])));
+      }
+    }
+  }
+}
+
+template <int W>
+__device__ __forceinline__ void all_reduce_body(const ArDev &d, const uint4 *in, uint4 *out, int n_vec, int *timed_out) {
+  const int b = blockIdx.x;
+  const uint32_t e = d.epoch[b] + 1;
+  const int parity = e & 1;
+  const int per = (n_vec + d.n_ctas - 1) / d.n_ctas;
+  const int lo = min(b * per, n_vec), hi = min(lo + per, n_vec);
+  char *me = d.peer[d.rank];
+  uint4 *stage = staging(me, d.max_bytes, parity);
+  for (int v = lo + threadIdx.x; v < hi; v += kArThreads) stage[v] = in[v];
+  bool ok = cta_barrier(d, false, e, timed_out);
+  if (n_vec <= d.one_shot_vecs || W == 2) {
+    if (ok) reduce_range<W>(d, parity, lo, hi, [&](int v, const uint4 &sum) { out[v] = sum; });
+  } else {
+    const int q = (hi - lo + W - 1) / W;
+    const int s_lo = min(lo + d.rank * q, hi), s_hi = min(s_lo + q, hi);
+    if (ok) {
+      uint4 *dst[W];
+#pragma unroll
+      for (int r = 0; r < W; ++r) dst[r] = result(d.peer[r], d.max_bytes, parity);
+      reduce_range<W>(d, parity, s_lo, s_hi, [&](int v, const uint4 &sum) {
+#pragma unroll
+        for (int r = 0; r < W; ++r) dst[r][v] = sum;
+      });
+    }
+    ok = cta_barrier(d, true, e, timed_out) && ok;
+    if (ok) {
+      const uint4 *res = result(me, d.max_bytes, parity);
+      for (int v = lo + threadIdx.x; v < hi; v += kArThreads) out[v] = ld_relaxed_sys(res + v);
+    }
+  }
+  if (threadIdx.x == 0) {
+    d.epoch[b] = e;
+    if (!ok) atomicExch(d.status, kArTimedOut);
+  }
+}
+
+__global__ void __launch_bounds__(kArThreads, 2) all_reduce_kernel(const __grid_constant__ ArLaunch L, int n_vec) {
+  __shared__ int timed_out;
+  const ArDev &d = L.dev[blockIdx.y];
+  const uint4 *in = static_cast<const uint4 *>(L.in[blockIdx.y]);
+  uint4 *out = static_cast<uint4 *>(L.out[blockIdx.y]);
+  if (threadIdx.x == 0) timed_out = 0;
+  switch (d.world) {
+    case 1: all_reduce_body<1>(d, in, out, n_vec, &timed_out); break;
+    case 2: all_reduce_body<2>(d, in, out, n_vec, &timed_out); break;
+    case 3: all_reduce_body<3>(d, in, out, n_vec, &timed_out); break;
+    case 4: all_reduce_body<4>(d, in, out, n_vec, &timed_out); break;
+    case 5: all_reduce_body<5>(d, in, out, n_vec, &timed_out); break;
+    case 6: all_reduce_body<6>(d, in, out, n_vec, &timed_out); break;
+    case 7: all_reduce_body<7>(d, in, out, n_vec, &timed_out); break;
+    default: all_reduce_body<8>(d, in, out, n_vec, &timed_out); break;
+  }
+}
+
+}  // namespace
+}  // namespace vt
+
+struct vt_ar {
+  vt::ArDev host;                 // travels by value with every launch
+  uint32_t *local = nullptr;      // device memory: epochs + status
+  int device = 0;
+};
+
+namespace {
+size_t shared_bytes(size_t max_bytes) { return 2 * vt::kArFlagBytes + 4 * max_bytes; }
+bool cuda_ok(cudaError_t e) { return e == cudaSuccess; }
+}  // namespace
+
+extern "C" {
+
+int vt_ar_buffer_bytes(size_t max_bytes, size_t *bytes) {
+  if (!bytes || max_bytes == 0 || max_bytes % 256 != 0) return VT_ERR_INVALID;
+  *bytes = shared_bytes(max_bytes);
+  return VT_OK;
+}
+
+int vt_ar_alloc(size_t bytes, void **buf) {
+  if (!buf || bytes == 0) return VT_ERR_INVALID;
+  void *p = nullptr;
+  if (!cuda_ok(cudaMalloc(&p, bytes))) return VT_ERR_CUDA;
+  if (!cuda_ok(cudaMemset(p, 0, bytes)) || !cuda_ok(cudaDeviceSynchronize())) {
+    cudaFree(p);
+    return VT_ERR_CUDA;
+  }
+  *buf = p;
+  return VT_OK;
+}
+
+int vt_ar_free(void *buf) { return cuda_ok(cudaFree(buf)) ? VT_OK : VT_ERR_CUDA; }
+
+int vt_ar_ipc_export(void *buf, unsigned char handle[64]) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  if (!buf || !handle) return VT_ERR_INVALID;
+  cudaIpcMemHandle_t h;
+  if (!cuda_ok(cudaIpcGetMemHandle(&h, buf))) return VT_ERR_CUDA;
+  memcpy(handle, &h, 64);
+  return VT_OK;
+}
+
+int vt_ar_ipc_open(const unsigned char handle[64], void **buf) {
+  if (!buf || !handle) return VT_ERR_INVALID;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  return cuda_ok(cudaIpcOpenMemHandle(buf, h, cudaIpcMemLazyEnablePeerAccess)) ? VT_OK : VT_ERR_CUDA;
+}
+
+int vt_ar_ipc_close(void *buf) { return cuda_ok(cudaIpcCloseMemHandle(buf)) ? VT_OK : VT_ERR_CUDA; }
+
+int vt_ar_create(int rank, int world, void *const *peer_bufs, size_t max_bytes, int n_ctas, vt_ar **out) {
+  if (!out || !peer_bufs || world < 1 || world > vt::kArMaxWorld || rank < 0 || rank >= world) return VT_ERR_INVALID;
+  if (max_bytes == 0 || max_bytes % 256 != 0 || max_bytes > (size_t(1) << 30)) return VT_ERR_INVALID;
+  if (n_ctas == 0) n_ctas = 32;
+  if (n_ctas < 1 || n_ctas > vt::kArMaxCtas) return VT_ERR_INVALID;
+  for (int r = 0; r < world; ++r)
+    if (!peer_bufs[r] || (reinterpret_cast<uintptr_t>(peer_bufs[r]) & 255) != 0) return VT_ERR_INVALID;
+  vt_ar *ar = new (std::nothrow) vt_ar();
+  if (!ar) return VT_ERR_CUDA;
+  if (!cuda_ok(cudaGetDevice(&ar->device)) ||
+      !cuda_ok(cudaMalloc(&ar->local, (vt::kArMaxCtas + 1) * sizeof(uint32_t))) ||
+      !cuda_ok(cudaMemset(ar->local, 0, (vt::kArMaxCtas + 1) * sizeof(uint32_t)))) {
+    cudaFree(ar->local);
+    delete ar;
+    return VT_ERR_CUDA;
+  }
+  vt::ArDev &h = ar->host;
+  h.rank = rank; h.world = world; h.n_ctas = n_ctas;
+  // One-shot (every rank reads everything) costs ~10 us + 1.8 us per MiB fetched from peers, two-shot ~19 us +
+  // 0.5 us per MiB of message (measured, 8 B200s): they cross where (world - 1) * bytes is about 6 MiB.
+  h.one_shot_vecs = world > 1 ? static_cast<int>(((6u << 20) / (world - 1)) / 16) : 0;
+  h.wait_ns = 1000000000ull;                                  // 1 s
+  h.max_bytes = max_bytes;
+  for (int r = 0; r < vt::kArMaxWorld; ++r) h.peer[r] = r < world ? static_cast<char *>(peer_bufs[r]) : nullptr;
+  h.epoch = ar->local;
+  h.status = ar->local + vt::kArMaxCtas;
+  *out = ar;
+  return VT_OK;
+}
+
+int vt_ar_destroy(vt_ar *ar) {
+  if (!ar) return VT_OK;
+  cudaFree(ar->local);
+  delete ar;
+  return VT_OK;
+}
+
+int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes) {
+  if (!ar) return VT_ERR_INVALID;
+  if (wait_ns > 0) ar->host.wait_ns = static_cast<unsigned long long>(wait_ns);
+  if (one_shot_bytes >= 0)
+    ar->host.one_shot_vecs = static_cast<int>(std::min<long long>(one_shot_bytes / 16, 1 << 30));
+  return VT_OK;
+}
+
+int vt_ar_status(vt_ar *ar, uint32_t *status) {
+  if (!ar || !status) return VT_ERR_INVALID;
+  return cuda_ok(cudaMemcpy(status, ar->host.status, sizeof(uint32_t), cudaMemcpyDeviceToHost)) ? VT_OK : VT_ERR_CUDA;
+}
+
+static int ar_checks(const vt_ar *ar, const void *in, const void *out, size_t n_elems) {
+  if (!ar || !in || !out) return VT_ERR_INVALID;
+  if (n_elems % 8 != 0 || ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) != 0)
+    return VT_ERR_UNSUPPORTED;
+  if (n_elems * 2 > ar->host.max_bytes) return VT_ERR_TOO_LARGE;
+  return VT_OK;
+}
+
+int vt_all_reduce(vt_ar *ar, const void *in, void *out, size_t n_elems, void *stream) {
+  if (n_elems == 0) return ar ? VT_OK : VT_ERR_INVALID;
+  const int st = ar_checks(ar, in, out, n_elems);
+  if (st != VT_OK) return st;
+  vt::ArLaunch L{};
+  L.dev[0] = ar->host; L.in[0] = in; L.out[0] = out;
+  vt::all_reduce_kernel<<<dim3(ar->host.n_ctas, 1), vt::kArThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      L, static_cast<int>(n_elems / 8));
+  return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;
+}
+
+int vt_all_reduce_emulated(vt_ar *const *ars, const void *const *ins, void *const *outs, int world, size_t n_elems,
+                           void *stream) {
+  if (!ars || !ins || !outs || world < 1 || world > vt::kArMaxWorld) return VT_ERR_INVALID;
+  if (n_elems == 0) return VT_OK;
+  vt::ArLaunch L{};
+  for (int r = 0; r < world; ++r) {
+    const int st = ar_checks(ars[r], ins[r], outs[r], n_elems);
+    if (st != VT_OK) return st;
+    if (ars[r]->host.world != world || ars[r]->host.rank != r || ars[r]->host.n_ctas != ars[0]->host.n_ctas)
+      return VT_ERR_INVALID;
+    L.dev[r] = ars[r]->host; L.in[r] = ins[r]; L.out[r] = outs[r];
+  }
+  int n_vec = static_cast<int>(n_elems / 8);
+  void *args[] = {&L, &n_vec};
+  // All ranks' CTAs wait on one another, so they must be resident together: a
+  // cooperative launch refuses (instead of hanging) when they do not fit.
+  const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void *>(vt::all_reduce_kernel),
+                                                    dim3(ars[0]->host.n_ctas, world), dim3(vt::kArThreads), args, 0,
+                                                    static_cast<cudaStream_t>(stream));
+  if (e == cudaErrorCooperativeLaunchTooLarge) return VT_ERR_TOO_LARGE;
+  return e == cudaSuccess ? VT_OK : VT_ERR_CUDA;
+}
+
+}  // extern "C"

@@ -12,7 +12,13 @@ select a kernel variant / partition size.
     python -m glake_b200.microbench rope TOKENS H KVH [fp8(0|1)] [iters]
     python -m glake_b200.microbench norm TOKENS HIDDEN [iters]
 
-time the element-wise steps either side of the attention: rotary embedding fused
+    torchrun --nproc-per-node N -m glake_b200.microbench allreduce [BYTES ...]
+
+times the peer-memory all-reduce against torch.distributed (NCCL) for bf16 messages
+of the given sizes (default 8 KiB .. 8 MiB): 100 calls captured in one CUDA graph,
+device time per call, max over ranks.
+
+The rope / norm modes time the element-wise steps either side of the attention: rotary embedding fused
 with the KV append (a prefill of TOKENS rows into one slot, or with TOKENS <= 1024
 a decode step of TOKENS entries), and rms_norm / fused_add_rms_norm.
 """
@@ -79,7 +85,60 @@ def norm_main():
     print(f"fused_add_rms_norm T{T} hidden{hidden}: {ms*1e3:.1f} us  {2*byt/ms/1e6:.0f} GB/s  ({2*byt/2**20:.1f} MiB)", flush=True)
 
 
+def allreduce_main():
+    import os
+    import torch.distributed as dist
+    from . import tp
+    rank = int(os.environ.get("LOCAL_RANK", 0))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+    world = dist.get_world_size()
+    sizes = [int(a) for a in sys.argv[2:]] or [8 << 10, 64 << 10, 128 << 10, 256 << 10, 1 << 20, 2 << 20, 8 << 20]
+    comm = tp.PeerAllReduce(max_size=max(max(sizes), 1 << 20))
+    if os.environ.get("VT_AR_ONE_SHOT_BYTES"):
+        comm.configure(one_shot_bytes=int(os.environ["VT_AR_ONE_SHOT_BYTES"]))
+    calls = 100
+    for nbytes in sizes:
+        x = torch.randn(nbytes // 2, device='cuda').bfloat16(); y = torch.empty_like(x)
+        res = {}
+        impls = [("peer", lambda: comm.all_reduce(x, y))]
+        if not os.environ.get("VT_AR_SKIP_NCCL"):
+            impls.append(("nccl", lambda: dist.all_reduce(x)))
+        if os.environ.get("VT_AR_SKIP_PEER"):
+            impls = impls[1:]
+        for name, fn in impls:
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for _ in range(3): fn()
+                side.synchronize()
+                g = torch.cuda.CUDAGraph()
+                # thread-local capture mode: the process group's watchdog thread may touch events meanwhile
+                with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+                    for _ in range(calls): fn()
+            ts = []
+            for _ in range(5):
+                dist.barrier(); torch.cuda.synchronize()
+                a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); g.replay(); z.record(); torch.cuda.synchronize()
+                ts.append(a.elapsed_time(z) * 1e3 / calls)
+            ts.sort()
+            res[name] = tp.max_over_ranks(ts[len(ts)//2], device='cuda')
+            del g                       # a live graph holding collective nodes stalls the teardown of the process group
+            torch.cuda.synchronize()
+        if rank == 0:
+            nccl, peer = res.get("nccl", float("nan")), res.get("peer", float("nan"))
+            print(f"all-reduce {world} ranks {nbytes >> 10:6d} KiB bf16: peer {peer:7.1f} us   nccl {nccl:7.1f} us   "
+                  f"x{nccl / peer:.2f}", flush=True)
+    st = comm.status()
+    comm.close()
+    if rank == 0:
+        print("status", st, flush=True)
+    dist.destroy_process_group()
+
+
 def main():
+    if sys.argv[1] == 'allreduce':
+        return allreduce_main()
     if sys.argv[1] == 'rope':
         return rope_main()
     if sys.argv[1] == 'norm':

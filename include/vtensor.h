@@ -41,7 +41,7 @@ enum {
   VT_ERR_STATE = 8,        /* call not valid in the object's current state */
   VT_ERR_NO_DRIVER = 9,    /* libcuda could not be loaded (no GPU on this machine) */
   VT_ERR_KERNEL = 10,      /* a kernel reported a bounded wait that ran out */
-  VT_ERR_TOO_LARGE = 11    /* problem needs more scratch than the built-in buffer of vt_decode_attn_static */
+  VT_ERR_TOO_LARGE = 11    /* problem exceeds a fixed built-in limit (scratch of vt_decode_attn_static, max_bytes of a vt_ar) */
 };
 
 /* Human-readable text for a status code (static storage). */
@@ -321,6 +321,58 @@ int vt_rms_norm(void *out, const void *input, const void *weight, float epsilon,
  * fp32 sums, the scaling from the sums after their rounding to bf16. */
 int vt_fused_add_rms_norm(void *input, void *residual, const void *weight, float epsilon, int num_tokens,
                           int hidden, void *stream);
+
+/* ---- low-latency all-reduce over NVLink peer memory ----------------------- */
+/* Sum all-reduce of small bf16 messages for the model-level reduction of a
+ * tensor-parallel layer (vllm/distributed/communication_op.py:57-84).  Replaces the
+ * reference's custom all-reduce (csrc/custom_all_reduce.cuh:182-247, :249-330;
+ * csrc/custom_all_reduce.cu:58-68, :116-135;
+ * vllm/distributed/device_communicators/custom_all_reduce.py:85, :155-165).
+ * One process per GPU; every rank owns one shared buffer that all ranks map:
+ *   vt_ar_buffer_bytes   size of that buffer for messages up to max_bytes
+ *                        (a multiple of 256)
+ *   vt_ar_alloc / free   allocate it zero-filled on the current device (cudaMalloc,
+ *                        so that it can be exported); any other zero-filled,
+ *                        256-byte aligned, peer-mappable memory works too
+ *   vt_ar_ipc_export / open / close   the CUDA IPC route to map it into the other
+ *                        processes; the 64-byte handles travel by any host channel
+ *   vt_ar_create         peer_bufs[r] = rank r's buffer as mapped in THIS process
+ *                        (own buffer at [rank]); n_ctas CTAs per call (0 = 32,
+ *                        at most 64), the same on every rank.  All ranks must
+ *                        have zero-filled their buffers before anybody's first call
+ *                        (a host barrier after creation).
+ *   vt_all_reduce        out = sum over ranks of in, n_elems bf16 (a multiple of 8,
+ *                        at most max_bytes / 2; VT_ERR_TOO_LARGE beyond), fp32
+ *                        accumulation in rank order, bit-identical on every rank;
+ *                        in may equal out.  Every rank must make the same sequence
+ *                        of calls.  One kernel launch, no host state per call:
+ *                        it may be captured into a CUDA graph.
+ *   vt_ar_status         0, or non-zero once a wait for a peer ran out of time
+ *                        (default 1 s; the results of that call are invalid and the
+ *                        communicator should be dropped); synchronises.
+ *   vt_ar_configure      wait limit in ns (<= 0 keeps it) and the message size up
+ *                        to which every rank reads everything itself (one-shot)
+ *                        instead of reduce-scatter + all-gather (< 0 keeps it;
+ *                        default 6 MiB / (world - 1); two ranks are always one-shot).
+ *   vt_all_reduce_emulated   runs all `world` ranks of one call as ONE cooperative
+ *                        launch on a single GPU (every vt_ar created on that GPU
+ *                        with the same peer_bufs): the way to exercise the protocol
+ *                        where fewer GPUs than ranks are available.
+ * Only plain peer loads and stores are used (no multimem, no TMA). */
+typedef struct vt_ar vt_ar;
+int vt_ar_buffer_bytes(size_t max_bytes, size_t *bytes);
+int vt_ar_alloc(size_t bytes, void **buf);
+int vt_ar_free(void *buf);
+int vt_ar_ipc_export(void *buf, unsigned char handle[64]);
+int vt_ar_ipc_open(const unsigned char handle[64], void **buf);
+int vt_ar_ipc_close(void *buf);
+int vt_ar_create(int rank, int world, void *const *peer_bufs, size_t max_bytes, int n_ctas, vt_ar **out);
+int vt_ar_destroy(vt_ar *ar);
+int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes);
+int vt_ar_status(vt_ar *ar, uint32_t *status);
+int vt_all_reduce(vt_ar *ar, const void *in, void *out, size_t n_elems, void *stream);
+int vt_all_reduce_emulated(vt_ar *const *ars, const void *const *ins, void *const *outs, int world,
+                           size_t n_elems, void *stream);
 
 /* vt_decode_attn for callers that cannot allocate device memory at all.
  * (No counterpart in the reference: its attention ops get their scratch from

@@ -197,6 +197,16 @@ def make_cos_sin_cache(max_position, rot_dim, base=10000.0):
     return torch.from_numpy(table).to(torch.bfloat16)
 
 
+def port_all_reduce(tensors):
+    """Sum of the ranks' bf16 tensors the way the reference's custom all-reduce forms
+    it (GLakeServe/csrc/custom_all_reduce.cuh:173-181): fp32 accumulation in rank
+    order, one rounding to bf16."""
+    acc = tensors[0].float()
+    for t in tensors[1:]:
+        acc = acc + t.float()
+    return acc.to(torch.bfloat16)
+
+
 def fill_ranges(k_list, v_list, range_bytes=None, k_scale=None, v_scale=None):
     """Build HostRanges holding the given per-sequence K/V ([L_i, KVH, D] bf16)
     by appending every row through the port's append (slot i = sequence i)."""

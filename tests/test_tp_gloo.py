@@ -46,6 +46,8 @@ def _worker(rank, world, port, h, kvh, ret):
         w = torch.ones(sh.num_heads * 128, 4)
         partial = out.view(3, -1).float() @ w
         tp.all_reduce_sum(partial)
+        same = tp.tensor_model_parallel_all_reduce(torch.full((4,), float(rank + 1)))   # no peer path on CPU: gloo
+        assert same.tolist() == [world * (world + 1) / 2] * 4
         slowest = tp.max_over_ranks(10.0 + rank)
         if rank == 0:
             rf = O.fill_ranges(k, v)
