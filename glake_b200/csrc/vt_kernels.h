@@ -19,6 +19,10 @@ struct SmemOptIn {
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
     if (set[dev].load(std::memory_order_relaxed) >= bytes) return true;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    // Without a stated preference the driver may pick a shared-memory carve-out that fits one CTA only.
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
+        cudaSuccess)
+      return false;
     set[dev].store(bytes, std::memory_order_relaxed);
     return true;
   }

@@ -37,7 +37,7 @@ constexpr int kPfTile = kBN * kPfPitch;      // one K (or V) tile
 constexpr int kPfStage = 2 * kPfTile;
 constexpr int kPfSmem = kPfStages * kPfStage + 2 * kPfStages * 8;
 
-__global__ void __launch_bounds__(kPfThreads) prefill_attn_kernel(PrefillParams p) {
+__global__ void __maxnreg__(168) prefill_attn_kernel(PrefillParams p) {
   extern __shared__ __align__(128) unsigned char smem[];
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kPfStages * kPfStage);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kPfStages);
