@@ -99,6 +99,9 @@ def _load():
                                    c_int, c_int, c_int, c_float, c_int, vp, vp, vp, vp, sz, ctypes.c_uint, vp]),
         "vt_prefill_attn": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                                     c_float, c_int, vp, vp]),
+        "vt_prefill_attn_tma": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
+                                        c_float, c_int, vp, vp, vp]),
+        "vt_prefill_maps_encode": (c_int, [vp, vp, c_int, c_int, c_int, c_uint64, vp]),
         "vt_decode_attn_static": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                                           c_float, c_int, vp, vp, vp, c_int, vp]),
         "vt_decode_attn_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int),

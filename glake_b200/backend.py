@@ -61,7 +61,22 @@ class VTensorCacheEngine:
             self.k_cache_ptr.append(torch.tensor(kp, dtype=torch.int64, device=self.device))
             self.v_cache_ptr.append(torch.tensor(vp, dtype=torch.int64, device=self.device))
 
+    def prefill_maps(self, layer):
+        """TMA tensor maps of this layer's ranges for ``ops.prefill_attention(..., maps=...)``
+        (built on first use; None when the kv-head count or cache dtype rules the path out)."""
+        if self.dtype_size != 2 or not ops.prefill_tma_supported(self.num_kv_heads):
+            return None
+        if not hasattr(self, "_prefill_maps"):
+            self._prefill_maps = {}
+        if layer not in self._prefill_maps:
+            segs = self.vmm_kvcache_segment
+            self._prefill_maps[layer] = ops.prefill_maps(
+                [s.getKeyDevicePtr(layer) for s in segs], [s.getValueDevicePtr(layer) for s in segs],
+                self.num_kv_heads, self.head_size, self.max_context_size // self.token_size, self.device)
+        return self._prefill_maps[layer]
+
     def close(self):
+        self._prefill_maps = {}
         for k, v in self.gpu_cache:
             k.kv_cache.close()
             v.kv_cache.close()

@@ -309,20 +309,52 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
                           key, value, key_stride, value_stride, byte_off, flags);
 }
 
-int vt_prefill_attn(void *out, int64_t out_stride, const void *q, int64_t q_stride, const uint64_t *k_table,
-                    const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
-                    const int32_t *q_lens, const int32_t *q_start, int batch, int h, int kvh, int d,
-                    int max_q_len, float scale, int kv_dtype, uint32_t *status, void *stream) {
+static int prefill_impl(void *out, int64_t out_stride, const void *q, int64_t q_stride, const uint64_t *k_table,
+                        const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
+                        const int32_t *q_lens, const int32_t *q_start, int batch, int h, int kvh, int d,
+                        int max_q_len, float scale, int kv_dtype, uint32_t *status, const void *maps, void *stream) {
   if (batch < 0 || h <= 0 || kvh <= 0 || max_q_len < 0) return VT_ERR_INVALID;
   if (batch == 0 || max_q_len == 0) return VT_OK;
   if (!out || !q || !k_table || !v_table || !slot_ids || !seq_lens || !q_lens || !q_start) return VT_ERR_INVALID;
   if (d != vt::kHeadDim || h % kvh != 0 || kv_dtype != VT_KV_BF16) return VT_ERR_UNSUPPORTED;
-  if ((reinterpret_cast<uintptr_t>(q) & 3) || (reinterpret_cast<uintptr_t>(out) & 3) || (q_stride % 2) || (out_stride % 2))
-    return VT_ERR_INVALID;
+  if ((reinterpret_cast<uintptr_t>(out) & 3) || (out_stride % 2)) return VT_ERR_INVALID;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (q_stride % 8)) return VT_ERR_UNSUPPORTED;   // q rows are read 16 bytes at a time
   if (q_stride < static_cast<int64_t>(h) * d || out_stride < static_cast<int64_t>(h) * d) return VT_ERR_INVALID;
+  if (maps) {
+    // Whole 32-token boxes are fetched even at the ragged end of a context, so a box must never
+    // straddle a 2 MiB chunk: rows per chunk (8192 / kvh) has to be a multiple of the box.
+    if ((reinterpret_cast<uintptr_t>(maps) & 63) != 0) return VT_ERR_INVALID;
+    if ((kvh & (kvh - 1)) != 0 || kvh * vt::kPrefillBoxTokens > 8192) return VT_ERR_UNSUPPORTED;
+  }
   vt::PrefillParams p{out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, q_lens, q_start,
-                      batch, h, kvh, scale, status};
+                      batch, h, kvh, scale, status, maps};
   return vt::launch_prefill_attn(p, max_q_len, static_cast<cudaStream_t>(stream));
+}
+
+int vt_prefill_attn(void *out, int64_t out_stride, const void *q, int64_t q_stride, const uint64_t *k_table,
+                    const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
+                    const int32_t *q_lens, const int32_t *q_start, int batch, int h, int kvh, int d,
+                    int max_q_len, float scale, int kv_dtype, uint32_t *status, void *stream) {
+  return prefill_impl(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, q_lens, q_start, batch, h,
+                      kvh, d, max_q_len, scale, kv_dtype, status, nullptr, stream);
+}
+
+int vt_prefill_attn_tma(void *out, int64_t out_stride, const void *q, int64_t q_stride, const uint64_t *k_table,
+                        const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
+                        const int32_t *q_lens, const int32_t *q_start, int batch, int h, int kvh, int d,
+                        int max_q_len, float scale, int kv_dtype, uint32_t *status, const void *maps, void *stream) {
+  if (!maps) return VT_ERR_INVALID;
+  return prefill_impl(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, q_lens, q_start, batch, h,
+                      kvh, d, max_q_len, scale, kv_dtype, status, maps, stream);
+}
+
+int vt_prefill_maps_encode(const uint64_t *k_bases, const uint64_t *v_bases, int n_slots, int kvh, int d,
+                           uint64_t max_tokens, void *host_maps) {
+  if (!k_bases || !v_bases || !host_maps || n_slots <= 0 || kvh <= 0 || max_tokens == 0) return VT_ERR_INVALID;
+  if ((reinterpret_cast<uintptr_t>(host_maps) & 63) != 0) return VT_ERR_INVALID;
+  if (d != vt::kHeadDim) return VT_ERR_UNSUPPORTED;
+  if ((kvh & (kvh - 1)) != 0 || kvh * vt::kPrefillBoxTokens > 8192 || max_tokens > 0xffffffffull) return VT_ERR_UNSUPPORTED;
+  return vt::encode_prefill_maps(k_bases, v_bases, n_slots, kvh, max_tokens, host_maps);
 }
 
 int vt_decode_attn_status(void *workspace, void *stream, int *code) {

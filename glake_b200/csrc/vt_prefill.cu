@@ -9,10 +9,12 @@
 // tokens [0, position].  Each consumer warp owns 16 query rows; the tile's Q rows
 // sit in shared memory (A fragments re-read per tile with ldmatrix, which keeps the
 // kernel at <= 128 registers so that four warps fit per scheduler).  A producer
-// warp streams K/V tiles of the head's kv head into a shared-memory ring with 1-D
-// bulk async copies (one 256-byte row per copy at a 272-byte pitch, which keeps
-// ldmatrix conflict free; the request-rate limit of small copies does not matter
-// here, the kernel is bound by issue slots and the tensor pipe, not by HBM).
+// warp streams 32-token K/V tiles of the head's kv head into a shared-memory ring,
+// either with TMA tensor copies through per-slot tensor maps (four requests per
+// tile, 128-byte swizzle: conflict-free ldmatrix without padding) or, without maps,
+// with one 1-D bulk copy per 256-byte row at a 272-byte pitch.  The row-copy form
+// is limited by the copy-request rate (measured: the consumers wait for data a third
+// of the time at 174 TFLOP/s), which is what the tensor copies remove.
 // Math per tile and warp, FlashAttention-2 style:
 //   S[16 q x BN tok] = Q . K^T     (mma.sync.m16n8k16 bf16, K^T via ldmatrix)
 //   causal mask only on tiles that reach past the warp's first row; tiles wholly
@@ -22,11 +24,14 @@
 //   O[16 q x 128]  += P . V        (P built 16 tokens at a time from the S
 //                                    accumulators as hi + lo bf16, V via ldmatrix.trans)
 // Roofline: tensor pipe (4 * q_len * L * 128 flops per head, half of that under
-// the causal mask); this kernel uses the legacy mma.sync path.
+// the causal mask); the math runs on the legacy mma.sync path (ncu: tensor pipe
+// 45 % busy at 174 TFLOP/s, so that path tops out near 390 TFLOP/s).
 #include "../../include/vtensor.h"
 #include "vt_device.cuh"
 #include "vt_kernels.h"
 #include "vt_mma.cuh"
+
+#include <cuda.h>
 
 #include <cstdlib>
 
@@ -35,27 +40,44 @@ namespace {
 
 constexpr int kPfPitch = 272;
 
-template <int WARPS, int BN_, int STAGES>
+// TMA = false: K/V rows arrive by one 256-byte bulk copy each at a 272-byte pitch.
+// TMA = true : a tile arrives by four tiled tensor copies (K and V, low and high 64 dims)
+//              through per-slot tensor maps; each lands as [BN rows][128 bytes] in the
+//              128-byte swizzle (16-byte chunk c of row r sits at chunk c ^ (r & 7)),
+//              which ldmatrix reads without bank conflicts and without padding.
+template <int WARPS, int BN_, int STAGES, bool TMA_ = false>
 struct PfCfg {
+  static constexpr bool kTma = TMA_;
   static constexpr int kWarps = WARPS;             // consumer warps
   static constexpr int kBM = WARPS * 16;           // query rows per CTA
   static constexpr int kBN = BN_;                  // tokens per K/V tile
   static constexpr int kStages = STAGES;
   static constexpr int kThreads = (WARPS + 1) * 32;
-  static constexpr int kTile = BN_ * kPfPitch;     // one K (or V) tile
+  static constexpr int kHalf = BN_ * 128;          // TMA: one 64-dim half of a K (or V) tile
+  static constexpr int kTile = TMA_ ? 2 * kHalf : BN_ * kPfPitch;     // one K (or V) tile
   static constexpr int kStage = 2 * kTile;
   static constexpr int kQBytes = kBM * kPfPitch;
-  static constexpr int kSmem = kQBytes + STAGES * kStage + 2 * STAGES * 8;
+  static constexpr int kRingPad = TMA_ ? 1024 : 0; // the swizzle pattern wants 1024-byte aligned tiles
+  static constexpr int kSmem = kQBytes + kRingPad + STAGES * kStage + 2 * STAGES * 8;
 };
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
 
 template <class C>
 __global__ void __maxnreg__(128) prefill_attn_kernel(PrefillParams p) {
   constexpr int kBM = C::kBM, kBN = C::kBN, kStages = C::kStages, kWarps = C::kWarps;
   constexpr int kTile = C::kTile, kStage = C::kStage;
   extern __shared__ __align__(128) unsigned char smem[];
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::kQBytes + kStages * kStage);
+  const uint32_t q0 = smem_u32(smem);
+  const uint32_t ring0 = C::kTma ? ((q0 + C::kQBytes + 1023u) & ~1023u) : q0 + C::kQBytes;
+  unsigned char *ring = smem + (ring0 - q0);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(ring + kStages * kStage);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
-  const uint32_t q0 = smem_u32(smem), ring0 = q0 + C::kQBytes;
 
   const int qt = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
   const int q_len = p.q_lens[b], seq_len = p.seq_lens[b];
@@ -89,14 +111,29 @@ __global__ void __maxnreg__(128) prefill_attn_kernel(PrefillParams p) {
         return;
       }
       const int t0 = tile * kBN;
-      const int nt = min(kBN, kv_end - t0);
-      if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2u * nt * 256);
-      __syncwarp();
-      for (int r = lane; r < nt; r += 32) {
-        const size_t goff = static_cast<size_t>(t0 + r) * tok_pitch;
-        const uint32_t dst = ring0 + s * kStage + r * kPfPitch;
-        bulk_g2s(dst, kbase + goff, 256, full0 + 8 * s);
-        bulk_g2s(dst + kTile, vbase + goff, 256, full0 + 8 * s);
+      if constexpr (C::kTma) {
+        // Whole boxes even on the ragged last tile: its rows past the context lie in the same
+        // mapped 2 MiB chunk (the host only takes this path when tiles never straddle chunks).
+        if (lane == 0) {
+          const char *maps = static_cast<const char *>(p.maps) + static_cast<size_t>(slot) * 256;
+          const uint32_t dst = ring0 + s * kStage, bar = full0 + 8 * s;
+          mbar_arrive_expect_tx(bar, 2u * kBN * 256);
+          tma_load_3d(dst, maps, 0, kv_head, t0, bar);
+          tma_load_3d(dst + C::kHalf, maps, 64, kv_head, t0, bar);
+          tma_load_3d(dst + kTile, maps + 128, 0, kv_head, t0, bar);
+          tma_load_3d(dst + kTile + C::kHalf, maps + 128, 64, kv_head, t0, bar);
+        }
+        __syncwarp();
+      } else {
+        const int nt = min(kBN, kv_end - t0);
+        if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2u * nt * 256);
+        __syncwarp();
+        for (int r = lane; r < nt; r += 32) {
+          const size_t goff = static_cast<size_t>(t0 + r) * tok_pitch;
+          const uint32_t dst = ring0 + s * kStage + r * kPfPitch;
+          bulk_g2s(dst, kbase + goff, 256, full0 + 8 * s);
+          bulk_g2s(dst + kTile, vbase + goff, 256, full0 + 8 * s);
+        }
       }
     }
     return;
@@ -133,9 +170,14 @@ __global__ void __maxnreg__(128) prefill_attn_kernel(PrefillParams p) {
   // Q as A operand (non-trans): matrices (rows 0-7, d lo), (rows 8-15, d lo), (rows 0-7, d hi), (rows 8-15, d hi)
   const uint32_t q_off = q0 + (warp * 16 + lr + ((li & 1) ? 8 : 0)) * kPfPitch + ((li >> 1) ? 16 : 0);
   // K^T as B operand (non-trans): matrices (tok 0-7, d lo), (tok 0-7, d hi), (tok 8-15, d lo), (tok 8-15, d hi)
-  const uint32_t k_off = (lr + ((li >> 1) ? 8 : 0)) * kPfPitch + ((li & 1) ? 16 : 0);
   // V as B operand (trans): matrices (tok 0-7, d 0-7), (tok 8-15, d 0-7), (tok 0-7, d 8-15), (tok 8-15, d 8-15)
-  const uint32_t v_off = kTile + (lr + ((li & 1) ? 8 : 0)) * kPfPitch + ((li >> 1) ? 16 : 0);
+  // Swizzled tiles: row pitch 128; 16-byte chunk (2m + bit) of a row with (row & 7) == lr sits at
+  // chunk (2m) ^ (bit ^ lr), so a lane's offset is its base XOR (m << 5), m = (16-dim step) & 3.
+  const uint32_t k_off = C::kTma ? (lr + ((li >> 1) ? 8 : 0)) * 128 + ((((li & 1) ^ lr) & 7) << 4)
+                                 : (lr + ((li >> 1) ? 8 : 0)) * kPfPitch + ((li & 1) ? 16 : 0);
+  const uint32_t v_off = C::kTma ? kTile + (lr + ((li & 1) ? 8 : 0)) * 128 + ((((li >> 1) ^ lr) & 7) << 4)
+                                 : kTile + (lr + ((li & 1) ? 8 : 0)) * kPfPitch + ((li >> 1) ? 16 : 0);
+  constexpr int kRowPitch = C::kTma ? 128 : kPfPitch;
 
   bool failed = false;
   for (int tile = 0; tile < n_tiles; ++tile) {
@@ -154,9 +196,14 @@ __global__ void __maxnreg__(128) prefill_attn_kernel(PrefillParams p) {
       // Ragged last tile: stale V rows would turn 0 * NaN into NaN.  Every warp clears
       // all of them itself (same zeros from every warp: a benign overlap) so that no
       // cross-warp barrier is needed inside the loop.
-      for (int r = nt + (lane >> 4); r < kBN; r += 2)
-        *reinterpret_cast<uint4 *>(smem + C::kQBytes + s * kStage + kTile + r * kPfPitch + (lane & 15) * 16) =
-            make_uint4(0, 0, 0, 0);
+      if constexpr (C::kTma) {
+        for (int r = nt + (lane >> 4); r < kBN; r += 2)     // 8 chunks in each 64-dim half, in any order
+          *reinterpret_cast<uint4 *>(ring + s * kStage + kTile + (lane & 8 ? C::kHalf : 0) + r * 128 + (lane & 7) * 16) =
+              make_uint4(0, 0, 0, 0);
+      } else {
+        for (int r = nt + (lane >> 4); r < kBN; r += 2)
+          *reinterpret_cast<uint4 *>(ring + s * kStage + kTile + r * kPfPitch + (lane & 15) * 16) = make_uint4(0, 0, 0, 0);
+      }
       __syncwarp();
     }
     // ---- S = Q . K^T : BN / 8 n-blocks of 8 tokens ----
@@ -170,7 +217,10 @@ __global__ void __maxnreg__(128) prefill_attn_kernel(PrefillParams p) {
 #pragma unroll
       for (int np = 0; np < kBN / 16; ++np) {   // 16 tokens per ldmatrix.x4
         uint32_t kb[4];
-        ldmatrix_x4(st + k_off + np * 16 * kPfPitch + ks * 32, kb);
+        if constexpr (C::kTma)
+          ldmatrix_x4(st + (ks >> 2) * C::kHalf + np * 16 * kRowPitch + (k_off ^ ((ks & 3) << 5)), kb);
+        else
+          ldmatrix_x4(st + k_off + np * 16 * kRowPitch + ks * 32, kb);
         mma_bf16(sacc[2 * np], qa, kb[0], kb[1]);
         mma_bf16(sacc[2 * np + 1], qa, kb[2], kb[3]);
       }
@@ -236,7 +286,10 @@ __global__ void __maxnreg__(128) prefill_attn_kernel(PrefillParams p) {
 #pragma unroll
       for (int dp = 0; dp < 8; ++dp) {   // 16 dims per ldmatrix.x4.trans
         uint32_t vb[4];
-        ldmatrix_x4_trans(st + v_off + kk * 16 * kPfPitch + dp * 32, vb);
+        if constexpr (C::kTma)
+          ldmatrix_x4_trans(st + (dp >> 2) * C::kHalf + kk * 16 * kRowPitch + (v_off ^ ((dp & 3) << 5)), vb);
+        else
+          ldmatrix_x4_trans(st + v_off + kk * 16 * kRowPitch + dp * 32, vb);
         mma_bf16(o[2 * dp], ph, vb[0], vb[1]);
         mma_bf16(o[2 * dp], pl, vb[0], vb[1]);
         mma_bf16(o[2 * dp + 1], ph, vb[2], vb[3]);
@@ -282,22 +335,49 @@ int launch_cfg(const PrefillParams &p, int max_q_len, cudaStream_t stream) {
 }
 
 int launch_prefill_attn(const PrefillParams &p, int max_q_len, cudaStream_t stream) {
-  // VT_PREFILL_CFG picks another tile shape (a tuning knob, like VT_ATTN_VARIANT for the decode kernels).
-  static const int cfg = [] {
-    const char *e = getenv("VT_PREFILL_CFG");
+  // Tensor copies: 64-row query tiles, three CTAs per SM (250 TFLOP/s causal at 4k prompts, 213 at 1k).
+  if (p.maps) return launch_cfg<PfCfg<4, 32, 3, true>>(p, max_q_len, stream);
+  // Row copies run into the copy-request rate (one request per 256-byte row): long prompts take
+  // 112-row tiles, which need 1.75 times fewer K/V requests per flop (204 vs 174 TFLOP/s at 4k);
+  // short ones lose more to ragged tiles than they gain.  VT_PREFILL_ROWS=64|112 forces a shape.
+  static const int forced = [] {
+    const char *e = getenv("VT_PREFILL_ROWS");
     return e ? atoi(e) : 0;
   }();
-  if (cfg == 0 && max_q_len > 1536)      // long prompts: 112-row tiles cut the K/V copy requests per flop by 1.75
-    return launch_cfg<PfCfg<7, 32, 3>>(p, max_q_len, stream);
-  switch (cfg) {
-    case 1: return launch_cfg<PfCfg<4, 64, 2>>(p, max_q_len, stream);   // 64 rows, 64-token tiles, 2 stages: 2 CTAs / SM
-    case 2: return launch_cfg<PfCfg<6, 64, 2>>(p, max_q_len, stream);   // 96 rows, 64-token tiles, 2 stages: 2 CTAs / SM
-    case 3: return launch_cfg<PfCfg<7, 32, 3>>(p, max_q_len, stream);   // 112 rows, 32-token tiles, 3 stages: 2 CTAs / SM
-    case 4: return launch_cfg<PfCfg<7, 64, 2>>(p, max_q_len, stream);   // 112 rows, 64-token tiles, 2 stages: 2 CTAs / SM
-    case 5: return launch_cfg<PfCfg<6, 32, 3>>(p, max_q_len, stream);   // 96 rows, 32-token tiles, 3 stages: 2 CTAs / SM
-    case 6: return launch_cfg<PfCfg<4, 32, 3>>(p, max_q_len, stream);
-    default: return launch_cfg<PfCfg<4, 32, 3>>(p, max_q_len, stream);  // 64 rows, 32-token tiles, 3 stages: 3 CTAs / SM
-  }
+  if (forced == 112 || (forced != 64 && max_q_len > 1536)) return launch_cfg<PfCfg<7, 32, 3>>(p, max_q_len, stream);
+  return launch_cfg<PfCfg<4, 32, 3>>(p, max_q_len, stream);
+}
+
+int encode_prefill_maps(const uint64_t *k_bases, const uint64_t *v_bases, int n_slots, int kvh, uint64_t max_tokens,
+                        void *host_maps) {
+  using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      fn = nullptr;
+    return reinterpret_cast<EncodeFn>(fn);
+  }();
+  if (!encode) return VT_ERR_NO_DRIVER;
+  // element (x, head, token) of a range: x fastest, heads 256 bytes apart, tokens kvh * 256 bytes apart
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(kHeadDim), static_cast<cuuint64_t>(kvh), max_tokens};
+  const cuuint64_t strides[2] = {256, static_cast<cuuint64_t>(kvh) * 256};
+  const cuuint32_t box[3] = {64, 1, static_cast<cuuint32_t>(kPrefillBoxTokens)};   // 128 bytes x 32 tokens of one head
+  const cuuint32_t elem_strides[3] = {1, 1, 1};
+  CUtensorMap *out = static_cast<CUtensorMap *>(host_maps);
+  for (int s = 0; s < n_slots; ++s)
+    for (int kv = 0; kv < 2; ++kv) {
+      const uint64_t base = kv ? v_bases[s] : k_bases[s];
+      if (base == 0 || (base & 15) != 0) return VT_ERR_INVALID;
+      if (encode(&out[2 * s + kv], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, reinterpret_cast<void *>(base), dims, strides, box,
+                 elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return VT_ERR_DRIVER;
+    }
+  return VT_OK;
 }
 
 }  // namespace vt

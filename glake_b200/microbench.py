@@ -12,6 +12,12 @@ select a kernel variant / partition size.
     python -m glake_b200.microbench rope TOKENS H KVH [fp8(0|1)] [iters]
     python -m glake_b200.microbench norm TOKENS HIDDEN [iters]
 
+    python -m glake_b200.microbench prefill B H KVH L [tma(0|1)] [iters]
+
+times causal prefill attention of B prompts of L tokens over their ranges (TFLOP/s
+of the causal half, 2 * B * H * L^2 * 128 flops), with K/V tiles fetched by TMA
+tensor copies (default) or by per-row bulk copies.
+
     torchrun --nproc-per-node N -m glake_b200.microbench allreduce [BYTES ...]
 
 times the peer-memory all-reduce against torch.distributed (NCCL) for bf16 messages
@@ -85,6 +91,31 @@ def norm_main():
     print(f"fused_add_rms_norm T{T} hidden{hidden}: {ms*1e3:.1f} us  {2*byt/ms/1e6:.0f} GB/s  ({2*byt/2**20:.1f} MiB)", flush=True)
 
 
+def prefill_main():
+    B,H,KVH,L = map(int, sys.argv[2:6])
+    tma = not (len(sys.argv)>6 and sys.argv[6]=='0')
+    iters = int(sys.argv[7]) if len(sys.argv)>7 else 10
+    torch.cuda.set_device(0); torch.zeros(1,device='cuda')
+    row = KVH*256
+    assert A.init_physical_handle(B*2*((L*row+(2<<20)-1)//(2<<20))+16, 0)
+    eng = VTensorCacheEngine(1, KVH, 128, B, L+8)
+    meta = VTensorMetadata(list(range(B)), [L]*B, KVH, 128, num_prefills=B); prepare_step(meta, eng)
+    k = torch.randn(B*L, KVH, 128, device='cuda', dtype=torch.bfloat16); v = torch.randn_like(k)
+    ops.reshape_and_cache(k, v, eng.k_cache_ptr[0], eng.v_cache_ptr[0], meta.slot_m, meta.slot_mapping, meta.seq_lens_tensor, meta.cache_seq_lens, L, KVH, 128)
+    q = torch.randn(B*L, H, 128, device='cuda', dtype=torch.bfloat16); out = torch.empty_like(q)
+    ql = torch.full((B,), L, dtype=torch.int32, device='cuda'); qs = torch.arange(B, dtype=torch.int32, device='cuda')*L
+    kc, vc = eng.gpu_cache[0]
+    maps = eng.prefill_maps(0) if tma else None
+    def run(): ops.prefill_attention(out, q, kc.vmm_ptr, vc.vmm_ptr, KVH, 128**-0.5, meta.slot_mapping, meta.seq_lens_tensor, ql, qs, L, maps=maps)
+    for _ in range(3): run()
+    torch.cuda.synchronize()
+    a,z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(); [run() for _ in range(iters)]; z.record(); torch.cuda.synchronize()
+    ms = a.elapsed_time(z)/iters
+    fl = 2*B*H*L*L*128
+    print(f"prefill B{B} H{H} KVH{KVH} L{L} {'tensor copies' if maps is not None else 'row copies'}: {ms:.3f} ms  {fl/ms/1e9:.1f} TFLOP/s (causal flops)", flush=True)
+
+
 def allreduce_main():
     import os
     import torch.distributed as dist
@@ -139,6 +170,8 @@ def allreduce_main():
 def main():
     if sys.argv[1] == 'allreduce':
         return allreduce_main()
+    if sys.argv[1] == 'prefill':
+        return prefill_main()
     if sys.argv[1] == 'rope':
         return rope_main()
     if sys.argv[1] == 'norm':

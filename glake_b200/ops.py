@@ -256,21 +256,47 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
               "vt_decode_step")
 
 
+def prefill_tma_supported(num_kv_heads):
+    """Whether ``prefill_maps`` / the TMA prefill path take this kv-head count (a
+    32-token box must never straddle a 2 MiB chunk)."""
+    return num_kv_heads & (num_kv_heads - 1) == 0 and num_kv_heads * 32 <= 8192
+
+
+def prefill_maps(k_bases, v_bases, num_kv_heads, head_size, max_tokens, device):
+    """Device table of TMA tensor maps for ``prefill_attention(..., maps=...)``:
+    ``k_bases[i]`` / ``v_bases[i]`` are slot i's range bases of one layer
+    (``getKeyDevicePtr`` / ``getValueDevicePtr``).  Valid while the slots live."""
+    n = len(k_bases)
+    kb = (ctypes.c_uint64 * n)(*[int(x) for x in k_bases])
+    vb = (ctypes.c_uint64 * n)(*[int(x) for x in v_bases])
+    host = torch.empty(n * 256 + 64, dtype=torch.uint8)
+    off = (-host.data_ptr()) % 64
+    with torch.cuda.device(device):
+        check(lib.vt_prefill_maps_encode(kb, vb, n, num_kv_heads, head_size, int(max_tokens),
+                                         c_void_p(host.data_ptr() + off)), "vt_prefill_maps_encode")
+    return host[off: off + n * 256].to(device)
+
+
 def prefill_attention(out, query, key_cache, value_cache, num_kv_heads, scale, slot_mapping, seq_lens, q_lens,
-                      q_start, max_q_len):
+                      q_start, max_q_len, maps=None):
     """Causal attention of the new tokens over the slots' whole ranges (the new rows
     already appended with ``reshape_and_cache``).  query/out ``[tokens, H, D]`` bf16,
     ``key_cache`` / ``value_cache`` the pointer-table addresses (ints), ``seq_lens``
-    the contexts including the new tokens, ``q_lens`` / ``q_start`` int32 per entry."""
-    _require_cuda(out, query, slot_mapping, seq_lens, q_lens, q_start)
+    the contexts including the new tokens, ``q_lens`` / ``q_start`` int32 per entry.
+    With ``maps`` (from :func:`prefill_maps`) K/V tiles are fetched by TMA tensor copies."""
+    _require_cuda(out, query, slot_mapping, seq_lens, q_lens, q_start, maps)
     if query.dtype != torch.bfloat16:
         raise RuntimeError("prefill_attention: bf16 only")
     n, num_heads, head_size = query.shape
+    args = (_ptr(out), out.stride(0), _ptr(query), query.stride(0), c_void_p(int(key_cache)),
+            c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens), _ptr(q_lens),
+            _ptr(q_start), slot_mapping.numel(), num_heads, num_kv_heads, head_size,
+            int(max_q_len), float(scale), VT_KV_BF16, None)
     with torch.cuda.device(query.device):
-        check(lib.vt_prefill_attn(_ptr(out), out.stride(0), _ptr(query), query.stride(0), c_void_p(int(key_cache)),
-                                  c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens), _ptr(q_lens),
-                                  _ptr(q_start), slot_mapping.numel(), num_heads, num_kv_heads, head_size,
-                                  int(max_q_len), float(scale), VT_KV_BF16, None, _stream()), "vt_prefill_attn")
+        if maps is None:
+            check(lib.vt_prefill_attn(*args, _stream()), "vt_prefill_attn")
+        else:
+            check(lib.vt_prefill_attn_tma(*args, _ptr(maps), _stream()), "vt_prefill_attn_tma")
 
 
 def attn_plan(batch, num_heads, num_kv_heads, max_seq_len, kv_cache_dtype="auto", num_splits=0):

@@ -270,11 +270,32 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
  *   q_start     device int32 [batch]: first row of entry i in q / out
  *   max_q_len   host upper bound of q_lens (sizes the grid)
  *   status      optional device word set to a non-zero magic if a bounded wait ran out; may be NULL
- * bf16 KV only; d must be 128. */
+ * bf16 KV only; d must be 128; q 16-byte aligned with a row stride that is a multiple of 8 elements. */
 int vt_prefill_attn(void *out, int64_t out_stride, const void *q, int64_t q_stride, const uint64_t *k_table,
                     const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
                     const int32_t *q_lens, const int32_t *q_start, int batch, int h, int kvh, int d,
                     int max_q_len, float scale, int kv_dtype, uint32_t *status, void *stream);
+
+/* vt_prefill_attn with the K/V tiles fetched by TMA tensor copies (one request
+ * per 32 tokens x 64 dims instead of one per token row), which lifts the
+ * copy-request limit the row-copy version runs into.  Same arguments plus
+ *   maps   device copy of the table vt_prefill_maps_encode filled: for every slot
+ *          id a K and a V tensor map (2 x 128 bytes per slot, 64-byte aligned).
+ * vt_prefill_maps_encode writes that table into HOST memory (n_slots x 256 bytes,
+ * 64-byte aligned; the caller copies it to the device once): k_bases / v_bases are
+ * the slots' range bases of one layer (vt_seg_k_ptr / vt_seg_v_ptr), max_tokens
+ * the rows a range is reserved for.  Bases never move, so the table stays valid
+ * while the slots live.  kvh must be a power of two <= 256 (a 32-token box may not
+ * straddle a 2 MiB chunk); VT_ERR_UNSUPPORTED otherwise — use vt_prefill_attn.
+ * No counterpart in the reference (its prefill runs in the external flash-attn fork). */
+#define VT_TMA_MAP_BYTES 128
+int vt_prefill_maps_encode(const uint64_t *k_bases, const uint64_t *v_bases, int n_slots, int kvh, int d,
+                           uint64_t max_tokens, void *host_maps);
+int vt_prefill_attn_tma(void *out, int64_t out_stride, const void *q, int64_t q_stride, const uint64_t *k_table,
+                        const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
+                        const int32_t *q_lens, const int32_t *q_start, int batch, int h, int kvh, int d,
+                        int max_q_len, float scale, int kv_dtype, uint32_t *status, const void *maps,
+                        void *stream);
 
 /* ---- element-wise steps either side of the attention --------------------- */
 /* Rotary embedding of q and k followed by the KV append, in one launch.

@@ -367,6 +367,14 @@ def test_prefill_attention_over_the_range(G, oracle, h, kvh):
                                         kvh, SCALE)
         ok, err = close_2e3(out.cpu(), port, ulp_slack=True)
         assert ok, err
+        # the same through TMA tensor copies: identical arithmetic, so identical bits
+        maps = kv.engine.prefill_maps(0)
+        assert maps is not None
+        out_t = torch.zeros_like(out)
+        ops.prefill_attention(out_t, q.cuda(), kv.k_table, kv.v_table, kvh, SCALE, kv.meta.slot_mapping,
+                              kv.meta.seq_lens_tensor, ql.cuda(), qs.cuda(), max(q_lens), maps=maps)
+        torch.cuda.synchronize()
+        assert torch.equal(out_t, out)
         # padded form: every sequence extends by the same 16 tokens
         s_new = 16
         lens2 = [n for n in lens if n >= s_new]
@@ -384,6 +392,38 @@ def test_prefill_attention_over_the_range(G, oracle, h, kvh):
                                          torch.arange(len(idx), dtype=torch.int32) * s_new, kvh, SCALE)
         ok, err = close_2e3(o2.cpu().view(-1, h, 128), port2, ulp_slack=True)
         assert ok, err
+    finally:
+        kv.close()
+
+
+@pytest.mark.parametrize("h,kvh", [(8, 2), (4, 4)])
+def test_prefill_long_prompts_both_copy_paths(G, oracle, h, kvh):
+    """Prompts beyond 1536 tokens take the 112-row tile shape; contexts end inside a
+    2 MiB chunk, at a tile edge and one row past a chunk boundary."""
+    from glake_b200 import ops
+    rows_per_chunk = (2 << 20) // (kvh * 256)
+    lens = [1700, rows_per_chunk + 1, 2048]
+    q_lens = [1700, 1601, 333]
+    _, k, v = synth.make_case(900 + kvh, lens, h, kvh)
+    rs = np.random.RandomState(9)
+    kv = G.GpuKV(k, v, kvh)
+    try:
+        starts = np.concatenate([[0], np.cumsum(q_lens)[:-1]]).astype(np.int32)
+        q = synth.normal_bf16(rs, int(sum(q_lens)), h, 128)
+        ql, qs = torch.tensor(q_lens, dtype=torch.int32), torch.from_numpy(starts)
+        r = oracle.fill_ranges(k, v)
+        port = oracle.port_prefill_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32), ql, qs,
+                                        kvh, SCALE)
+        outs = []
+        for maps in (None, kv.engine.prefill_maps(0)):
+            out = torch.zeros_like(q, device="cuda")
+            ops.prefill_attention(out, q.cuda(), kv.k_table, kv.v_table, kvh, SCALE, kv.meta.slot_mapping,
+                                  kv.meta.seq_lens_tensor, ql.cuda(), qs.cuda(), max(q_lens), maps=maps)
+            torch.cuda.synchronize()
+            ok, err = close_2e3(out.cpu(), port, ulp_slack=True)
+            assert ok, err
+            outs.append(out)
+        assert torch.equal(outs[0], outs[1])
     finally:
         kv.close()
 
