@@ -10,7 +10,8 @@ namespace vt {
 
 constexpr int kHeadDim = 128;
 constexpr uint32_t kKernelErrMagic = 0xDEAD0A77u;  // value of the workspace status word after a failed wait
-constexpr uint32_t kWaitLimit = 1u << 22;          // try_wait rounds before a wait gives up
+constexpr uint32_t kWaitLimit = 1u << 22;          // try_wait rounds before a wait gives up ...
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;   // ... or one second, whichever comes first
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -39,10 +40,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: false when the phase did not complete within kWaitLimit rounds.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: false when the phase did not complete within kWaitLimitNs of wall time
+// (a try_wait round may itself block for a hardware-defined time, so rounds are not
+// counted; the clock is read only after a round that failed).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-  for (uint32_t it = 0; it < kWaitLimit; ++it)
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+  }
   return false;
 }
 

@@ -87,6 +87,7 @@ struct PrefillParams {
   const void *maps;                   // optional device table [slot][K, V] of 128-byte TMA tensor maps
 };
 int launch_prefill_attn(const PrefillParams &p, int max_q_len, cudaStream_t stream);
+int launch_prefill_umma(const PrefillParams &p, int max_q_len, cudaStream_t stream);   // needs p.maps
 constexpr int kPrefillBoxTokens = 32; // token extent of the tensor maps' box (= the kernel's K/V tile)
 // Fills host_maps[slot][K, V] (128 bytes each, 64-byte aligned) for ranges of kvh heads and max_tokens rows.
 int encode_prefill_maps(const uint64_t *k_bases, const uint64_t *v_bases, int n_slots, int kvh, uint64_t max_tokens,

@@ -1,0 +1,296 @@
+// Causal prefill / prefix-extend attention on the 5th-generation tensor cores:
+// tcgen05.mma with operands in shared memory and accumulators in tensor memory.
+// Same contract and arithmetic as the mma.sync kernel of vt_prefill.cu (fp32 softmax,
+// P applied as hi + lo bf16 halves), needs the per-slot TMA tensor maps.
+//
+// One CTA per (128-query tile, q head, sequence), six warps:
+//   warps 0-3  softmax: thread = query row = TMEM lane.  Reads its row of S with
+//              tcgen05.ld (no shuffles: the row's max and sum live in one thread),
+//              writes P (hi and lo) into shared memory in the K-major 128-byte swizzle,
+//              rescales its row of O in TMEM only when the running maximum grew by more
+//              than 2^8 (P then stays <= 256, harmless in fp32), and at the end
+//              normalises and stores the row.
+//   warp 4     producer: one lane issues the TMA tensor copies of the 64-token K/V
+//              tiles (two 32-token boxes per 64-dim half) into a shared-memory ring.
+//   warp 5     one lane issues the MMAs: S = Q.K^T (8 steps of K = 16, N = 64) into TMEM
+//              columns [0, 64); O += P_hi.V + P_lo.V (2 x 4 steps, N = 128, V as the
+//              MN-major operand) into columns [64, 192); tcgen05.commit signals the
+//              mbarriers the other roles wait on.
+// Hand-offs (mbarriers, every wait bounded): kv_full / kv_empty per ring stage,
+// s_full (S ready), p_full (P written and S consumed; 128 arrivals), o_full (P.V of
+// the tile done: P may be overwritten, O may be rescaled or read).
+// Shared memory: Q 32 KB + ring 2 x 32 KB + P 32 KB = 128 KB; TMEM: 256 columns.
+#include "../../include/vtensor.h"
+#include "vt_device.cuh"
+#include "vt_kernels.h"
+#include "vt_umma.cuh"
+
+namespace vt {
+namespace {
+
+constexpr int kUM = 128;                 // query rows per CTA
+constexpr int kUN = 64;                  // tokens per K/V tile
+constexpr int kUStages = 2;
+constexpr int kUThreads = 192;
+constexpr int kQSlab = kUM * 128;        // one 64-dim half of Q: [128 rows][128 B]
+constexpr int kKVSlab = kUN * 128;       // one 64-dim half of a K (or V) tile: [64 tokens][128 B]
+constexpr int kUStage = 4 * kKVSlab;     // K lo, K hi, V lo, V hi
+constexpr int kPSlab = kUM * 128;        // P hi (or lo): [128 rows][64 tokens]
+constexpr int kUSmem = 1024 + 2 * kQSlab + kUStages * kUStage + 2 * kPSlab + 64;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kColS = 0, kColO = 64;
+constexpr float kRescaleGap = 8.f;       // log2 units
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t *>(&v);
+}
+
+__global__ void __launch_bounds__(kUThreads, 1) prefill_umma_kernel(PrefillParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  unsigned char *sm = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t q_s = base, ring_s = q_s + 2 * kQSlab, p_s = ring_s + kUStages * kUStage;
+  unsigned char *q_g = sm, *ring_g = sm + 2 * kQSlab, *p_g = ring_g + kUStages * kUStage;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(p_g + 2 * kPSlab);
+  const uint32_t kv_full = smem_u32(bars), kv_empty = kv_full + 8 * kUStages, s_full = kv_empty + 8 * kUStages,
+                 p_full = s_full + 8, o_full = p_full + 8, q_full = o_full + 8;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int failed;
+
+  const int qt = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+  const int q_len = p.q_lens[b], seq_len = p.seq_lens[b];
+  const int j0 = qt * kUM;
+  if (j0 >= q_len) return;                                  // whole CTA: nothing allocated yet
+  const int g = p.h / p.kvh, kv_head = hq / g;
+  const int pos0 = seq_len - q_len + j0;                    // position of the tile's first query row
+  const int kv_end = min(seq_len, pos0 + kUM);              // keys any row of the tile may see
+  const int n_tiles = (kv_end + kUN - 1) / kUN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (tid == 0) {
+    for (int s = 0; s < kUStages; ++s) {
+      mbar_init(kv_full + 8 * s, 1);
+      mbar_init(kv_empty + 8 * s, 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_full, kUM);
+    mbar_init(o_full, 1);
+    mbar_init(q_full, kUM);
+    mbar_fence_init();
+    failed = 0;
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem = tmem_slot;
+
+  if (warp == 4) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      const int64_t slot = p.slot_ids[b];
+      const char *maps = static_cast<const char *>(p.maps) + static_cast<size_t>(slot) * 256;
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j % kUStages;
+        if (j >= kUStages && !mbar_wait(kv_empty + 8 * s, ((j / kUStages) - 1) & 1)) { failed = 1; break; }
+        const int t0 = j * kUN;
+        const int boxes = (kv_end - t0 > 32) ? 2 : 1;       // the second 32-token box only if it holds context
+        const uint32_t dst = ring_s + s * kUStage, bar = kv_full + 8 * s;
+        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(boxes) * 4u * 4096u);
+        for (int bx = 0; bx < boxes; ++bx) {
+          const int z = t0 + 32 * bx;
+          const uint32_t d = dst + bx * 4096;
+          tma_load_3d(d, maps, 0, kv_head, z, bar);
+          tma_load_3d(d + kKVSlab, maps, 64, kv_head, z, bar);
+          tma_load_3d(d + 2 * kKVSlab, maps + 128, 0, kv_head, z, bar);
+          tma_load_3d(d + 3 * kKVSlab, maps + 128, 64, kv_head, z, bar);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc_qk = umma_idesc_bf16_f32(kUM, kUN, false, false);
+      const uint32_t idesc_pv = umma_idesc_bf16_f32(kUM, kHeadDim, false, true);
+      bool ok = mbar_wait(q_full, 0);
+      tcgen05_fence_after();
+      auto issue_qk = [&](int j) {
+        const uint32_t st = ring_s + (j % kUStages) * kUStage;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t da = umma_desc_sw128(q_s + (kk >> 2) * kQSlab + (kk & 3) * 32, 0, 1024);
+          const uint64_t db = umma_desc_sw128(st + (kk >> 2) * kKVSlab + (kk & 3) * 32, 0, 1024);
+          umma_bf16(tmem + kColS, da, db, idesc_qk, kk > 0);
+        }
+        umma_commit(s_full);
+      };
+      if (ok) ok = mbar_wait(kv_full, 0);
+      if (ok) {
+        tcgen05_fence_after();
+        issue_qk(0);
+      }
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        if (!mbar_wait(p_full, j & 1)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t st = ring_s + (j % kUStages) * kUStage + 2 * kKVSlab;      // V of this tile
+#pragma unroll
+        for (int half = 0; half < 2; ++half)
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t da = umma_desc_sw128(p_s + half * kPSlab + kk * 32, 0, 1024);
+            const uint64_t db = umma_desc_sw128(st + kk * 16 * 128, /*next 64 dims*/ kKVSlab, /*next 8 tokens*/ 1024);
+            umma_bf16(tmem + kColO, da, db, idesc_pv, j > 0 || half > 0 || kk > 0);
+          }
+        umma_commit(kv_empty + 8 * (j % kUStages));       // the stage may be refilled ...
+        umma_commit(o_full);                              // ... and P / O belong to the softmax warps again
+        if (j + 1 < n_tiles) {
+          const int s1 = (j + 1) % kUStages;
+          if (!mbar_wait(kv_full + 8 * s1, ((j + 1) / kUStages) & 1)) { ok = false; break; }
+          tcgen05_fence_after();
+          issue_qk(j + 1);
+        }
+      }
+      if (!ok) failed = 1;
+    }
+  } else {
+    // ---------------- softmax warps: thread = query row ----------------
+    const int row = warp * 32 + lane;                       // row of the tile = TMEM lane
+    const int jrow = j0 + row;                              // entry-relative query index
+    const bool row_ok = jrow < q_len;
+    const int lim = pos0 + row;                             // last visible token
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    {  // Q row -> shared memory (zeros beyond q_len), K-major 128-byte swizzle, two 64-dim slabs
+      const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.q) +
+                                                         (static_cast<int64_t>(p.q_start[b]) + jrow) * p.q_stride + hq * kHeadDim);
+#pragma unroll
+      for (int c = 0; c < 16; ++c) {
+        const uint4 v = row_ok ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4 *>(q_g + (c >> 3) * kQSlab + sw128_offset(row, c & 7)) = v;
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(q_full);
+    }
+    const float sl2 = p.scale * 1.4426950408889634f;
+    float m_ref = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full, j & 1))) { ok = false; break; }   // warp-uniform: tcgen05.ld follows
+      tcgen05_fence_after();
+      float x[kUN];
+#pragma unroll
+      for (int c0 = 0; c0 < kUN; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + kColS + c0, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) x[c0 + i] = __uint_as_float(v[i]) * sl2;
+      }
+      const int t0 = j * kUN;
+      float mx = -INFINITY;
+      if (t0 + kUN - 1 > lim) {
+#pragma unroll
+        for (int i = 0; i < kUN; ++i) x[i] = (t0 + i <= lim) ? x[i] : -INFINITY;
+      }
+#pragma unroll
+      for (int i = 0; i < kUN; ++i) mx = fmaxf(mx, x[i]);
+      // P of the previous tile must have been consumed before it is overwritten, and O must be
+      // quiescent before it is rescaled: both are what o_full of the previous tile says.
+      if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(o_full, (j - 1) & 1))) { ok = false; break; }
+      tcgen05_fence_after();
+      // tcgen05.ld / .st are warp-wide instructions: the decision to rescale is taken per warp,
+      // every lane then moves its reference to max(old, tile) (a factor of 1 where nothing changed).
+      if (__any_sync(0xffffffffu, mx > m_ref + kRescaleGap || (m_ref == -INFINITY && mx != -INFINITY))) {
+        const float m_new = fmaxf(m_ref, mx);
+        const float f = m_ref == -INFINITY ? 1.f : exp2f(m_ref - m_new);      // O is still empty while m_ref is -inf
+        l *= f;
+        if (j > 0) {
+#pragma unroll
+          for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(lane_addr + kColO + c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+            tmem_st_32x32b_x32(lane_addr + kColO + c0, v);
+          }
+          tmem_st_wait();
+        }
+        m_ref = m_new;
+      }
+      const float ref = m_ref == -INFINITY ? 0.f : m_ref;    // nothing visible yet: every x is -inf, every p is 0
+      if (kv_end - t0 < kUN) {
+        // Ragged last tile: V rows past the context may hold anything (0 * NaN = NaN).  The rows of
+        // this thread's share are cleared in both 64-dim halves before the tensor core reads them.
+        if (!__all_sync(0xffffffffu, mbar_wait(kv_full + 8 * (j % kUStages), (j / kUStages) & 1))) { ok = false; break; }
+        unsigned char *vst = ring_g + (j % kUStages) * kUStage + 2 * kKVSlab;
+        for (int r = (kv_end - t0) + (row >> 4); r < kUN; r += 8)
+          *reinterpret_cast<uint4 *>(vst + ((row >> 3) & 1) * kKVSlab + r * 128 + (row & 7) * 16) = make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {                         // 8 tokens per 16-byte chunk
+        uint32_t hi[4], lo[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p0 = exp2f(x[c * 8 + 2 * e] - ref), p1 = exp2f(x[c * 8 + 2 * e + 1] - ref);
+          l += p0 + p1;
+          hi[e] = pack_bf16x2(p0, p1);
+          lo[e] = pack_bf16x2(p0 - bf16_lo(hi[e]), p1 - bf16_hi(hi[e]));
+        }
+        const uint32_t off = sw128_offset(row, c);
+        *reinterpret_cast<uint4 *>(p_g + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        *reinterpret_cast<uint4 *>(p_g + kPSlab + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+      }
+      fence_proxy_async_smem();
+      tcgen05_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok && !__all_sync(0xffffffffu, mbar_wait(o_full, (n_tiles - 1) & 1))) ok = false;
+    tcgen05_fence_after();
+    if (__all_sync(0xffffffffu, ok)) {                      // warp-wide TMEM loads; only the stores are per row
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      uint4 *dst = reinterpret_cast<uint4 *>(static_cast<__nv_bfloat16 *>(p.out) +
+                                             (static_cast<int64_t>(p.q_start[b]) + jrow) * p.out_stride + hq * kHeadDim);
+#pragma unroll
+      for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32b_x32(lane_addr + kColO + c0, v);
+        tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            dst[c0 / 8 + i] = make_uint4(pack_bf16x2(__uint_as_float(v[8 * i]) * inv, __uint_as_float(v[8 * i + 1]) * inv),
+                                         pack_bf16x2(__uint_as_float(v[8 * i + 2]) * inv, __uint_as_float(v[8 * i + 3]) * inv),
+                                         pack_bf16x2(__uint_as_float(v[8 * i + 4]) * inv, __uint_as_float(v[8 * i + 5]) * inv),
+                                         pack_bf16x2(__uint_as_float(v[8 * i + 6]) * inv, __uint_as_float(v[8 * i + 7]) * inv));
+        }
+      }
+    }
+    if (!ok) failed = 1;
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, kTmemCols);
+  if (tid == 0 && failed && p.status) atomicExch(p.status, kKernelErrMagic);
+}
+
+}  // namespace
+
+int launch_prefill_umma(const PrefillParams &p, int max_q_len, cudaStream_t stream) {
+  static SmemOptIn opt_in;
+  if (!opt_in.ensure(prefill_umma_kernel, kUSmem)) return VT_ERR_CUDA;
+  dim3 grid((max_q_len + kUM - 1) / kUM, p.h, p.batch);
+  prefill_umma_kernel<<<grid, kUThreads, kUSmem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;
+}
+
+}  // namespace vt

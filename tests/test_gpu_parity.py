@@ -16,6 +16,7 @@ from tests import synth
 from tests.test_oracle import SCALE, load_golden
 
 pytestmark = pytest.mark.gpu
+UMMA = os.environ.get("VT_PREFILL_ENGINE", "").startswith("u")   # tcgen05 prefill kernel selected
 
 
 def close_2e3(a, b, ulp_slack=False):
@@ -374,7 +375,10 @@ def test_prefill_attention_over_the_range(G, oracle, h, kvh):
         ops.prefill_attention(out_t, q.cuda(), kv.k_table, kv.v_table, kvh, SCALE, kv.meta.slot_mapping,
                               kv.meta.seq_lens_tensor, ql.cuda(), qs.cuda(), max(q_lens), maps=maps)
         torch.cuda.synchronize()
-        assert torch.equal(out_t, out)
+        ok, err = close_2e3(out_t.cpu(), port, ulp_slack=True)
+        assert ok, err
+        if not UMMA:                     # the mma.sync kernel does identical arithmetic on both copy paths
+            assert torch.equal(out_t, out)
         # padded form: every sequence extends by the same 16 tokens
         s_new = 16
         lens2 = [n for n in lens if n >= s_new]
@@ -423,7 +427,8 @@ def test_prefill_long_prompts_both_copy_paths(G, oracle, h, kvh):
             ok, err = close_2e3(out.cpu(), port, ulp_slack=True)
             assert ok, err
             outs.append(out)
-        assert torch.equal(outs[0], outs[1])
+        if not UMMA:
+            assert torch.equal(outs[0], outs[1])
     finally:
         kv.close()
 
