@@ -336,15 +336,15 @@ int launch_cfg(const PrefillParams &p, int max_q_len, cudaStream_t stream) {
 
 int launch_prefill_attn(const PrefillParams &p, int max_q_len, cudaStream_t stream) {
   if (p.maps) {
-    // VT_PREFILL_ENGINE=umma|mma picks the tcgen05 kernel or the mma.sync one.
-    static const int engine = [] {
+    // The tcgen05 kernel (vt_prefill_umma.cu) is the default with tensor maps; VT_PREFILL_ENGINE=mma
+    // keeps the mma.sync kernel.  The tcgen05 kernel fetches 64-token tiles (no straddling of a
+    // 2 MiB chunk: kvh <= 128) and stores whole 16-byte vectors of the output rows.
+    static const bool legacy = [] {
       const char *e = getenv("VT_PREFILL_ENGINE");
-      return e && e[0] == 'u' ? 1 : 0;
+      return e && e[0] == 'm';
     }();
-    // The tcgen05 kernel fetches 64-token tiles (no straddling of a 2 MiB chunk: kvh <= 128) and
-    // stores whole 16-byte vectors of the output rows.
     const bool umma_ok = p.kvh * 64 <= 8192 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 && p.out_stride % 8 == 0;
-    if (engine == 1 && umma_ok) return launch_prefill_umma(p, max_q_len, stream);
+    if (!legacy && umma_ok) return launch_prefill_umma(p, max_q_len, stream);
     // mma.sync with tensor copies: 64-row query tiles, three CTAs per SM (250 TFLOP/s causal at 4k prompts, 213 at 1k).
     return launch_cfg<PfCfg<4, 32, 3, true>>(p, max_q_len, stream);
   }

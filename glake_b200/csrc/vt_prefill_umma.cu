@@ -6,20 +6,21 @@
 // One CTA per (128-query tile, q head, sequence), six warps:
 //   warps 0-3  softmax: thread = query row = TMEM lane.  Reads its row of S with
 //              tcgen05.ld (no shuffles: the row's max and sum live in one thread),
-//              writes P (hi and lo) into shared memory in the K-major 128-byte swizzle,
+//              writes P (hi and lo bf16 halves) back over the same TMEM columns,
 //              rescales its row of O in TMEM only when the running maximum grew by more
 //              than 2^8 (P then stays <= 256, harmless in fp32), and at the end
 //              normalises and stores the row.
 //   warp 4     producer: one lane issues the TMA tensor copies of the 64-token K/V
 //              tiles (two 32-token boxes per 64-dim half) into a shared-memory ring.
-//   warp 5     one lane issues the MMAs: S = Q.K^T (8 steps of K = 16, N = 64) into TMEM
-//              columns [0, 64); O += P_hi.V + P_lo.V (2 x 4 steps, N = 128, V as the
-//              MN-major operand) into columns [64, 192); tcgen05.commit signals the
-//              mbarriers the other roles wait on.
+//   warp 5     one lane issues the MMAs: S = Q.K^T (8 steps of K = 16, N = 64) into one of
+//              two 64-column S/P buffers, so that the product of tile j+1 runs while the
+//              softmax warps work on tile j; O += P_hi.V + P_lo.V (2 x 4 steps, N = 128,
+//              P read from TMEM as the A operand, V as the MN-major B operand) into
+//              columns [128, 256); tcgen05.commit signals the mbarriers the others wait on.
 // Hand-offs (mbarriers, every wait bounded): kv_full / kv_empty per ring stage,
-// s_full (S ready), p_full (P written and S consumed; 128 arrivals), o_full (P.V of
-// the tile done: P may be overwritten, O may be rescaled or read).
-// Shared memory: Q 32 KB + ring 2 x 32 KB + P 32 KB = 128 KB; TMEM: 256 columns.
+// s_full / p_full per S/P buffer (S ready; P written, 128 arrivals), o_full (P.V of
+// a tile done: O may be rescaled or read).
+// Shared memory: Q 32 KB + ring 2 x 32 KB = 96 KB and 256 TMEM columns: two CTAs per SM.
 #include "../../include/vtensor.h"
 #include "vt_device.cuh"
 #include "vt_kernels.h"
@@ -35,10 +36,9 @@ constexpr int kUThreads = 192;
 constexpr int kQSlab = kUM * 128;        // one 64-dim half of Q: [128 rows][128 B]
 constexpr int kKVSlab = kUN * 128;       // one 64-dim half of a K (or V) tile: [64 tokens][128 B]
 constexpr int kUStage = 4 * kKVSlab;     // K lo, K hi, V lo, V hi
-constexpr int kPSlab = kUM * 128;        // P hi (or lo): [128 rows][64 tokens]
-constexpr int kUSmem = 1024 + 2 * kQSlab + kUStages * kUStage + 2 * kPSlab + 64;
+constexpr int kUSmem = 1024 + 2 * kQSlab + kUStages * kUStage + 128;
 constexpr uint32_t kTmemCols = 256;
-constexpr uint32_t kColS = 0, kColO = 64;
+constexpr uint32_t kColS = 0, kColO = 128;   // S/P buffer b at columns [64 b, 64 b + 64): P hi over the first 32, P lo over the rest
 constexpr float kRescaleGap = 8.f;       // log2 units
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *map, int x, int y, int z, uint32_t bar) {
@@ -52,15 +52,15 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *reinterpret_cast<uint32_t *>(&v);
 }
 
-__global__ void __launch_bounds__(kUThreads, 1) prefill_umma_kernel(PrefillParams p) {
+__global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   unsigned char *sm = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t q_s = base, ring_s = q_s + 2 * kQSlab, p_s = ring_s + kUStages * kUStage;
-  unsigned char *q_g = sm, *ring_g = sm + 2 * kQSlab, *p_g = ring_g + kUStages * kUStage;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(p_g + 2 * kPSlab);
+  const uint32_t q_s = base, ring_s = q_s + 2 * kQSlab;
+  unsigned char *q_g = sm, *ring_g = sm + 2 * kQSlab;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(ring_g + kUStages * kUStage);
   const uint32_t kv_full = smem_u32(bars), kv_empty = kv_full + 8 * kUStages, s_full = kv_empty + 8 * kUStages,
-                 p_full = s_full + 8, o_full = p_full + 8, q_full = o_full + 8;
+                 p_full = s_full + 16, o_full = p_full + 16, q_full = o_full + 8;
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
@@ -79,8 +79,10 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_umma_kernel(PrefillParam
       mbar_init(kv_full + 8 * s, 1);
       mbar_init(kv_empty + 8 * s, 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(p_full, kUM);
+    for (int bf = 0; bf < 2; ++bf) {
+      mbar_init(s_full + 8 * bf, 1);
+      mbar_init(p_full + 8 * bf, kUM);
+    }
     mbar_init(o_full, 1);
     mbar_init(q_full, kUM);
     mbar_fence_init();
@@ -124,40 +126,42 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_umma_kernel(PrefillParam
       const uint32_t idesc_pv = umma_idesc_bf16_f32(kUM, kHeadDim, false, true);
       bool ok = mbar_wait(q_full, 0);
       tcgen05_fence_after();
-      auto issue_qk = [&](int j) {
+      auto issue_qk = [&](int j) {                          // S of tile j -> buffer j & 1
         const uint32_t st = ring_s + (j % kUStages) * kUStage;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint64_t da = umma_desc_sw128(q_s + (kk >> 2) * kQSlab + (kk & 3) * 32, 0, 1024);
           const uint64_t db = umma_desc_sw128(st + (kk >> 2) * kKVSlab + (kk & 3) * 32, 0, 1024);
-          umma_bf16(tmem + kColS, da, db, idesc_qk, kk > 0);
+          umma_bf16(tmem + kColS + (j & 1) * 64, da, db, idesc_qk, kk > 0);
         }
-        umma_commit(s_full);
+        umma_commit(s_full + 8 * (j & 1));
       };
-      if (ok) ok = mbar_wait(kv_full, 0);
-      if (ok) {
-        tcgen05_fence_after();
-        issue_qk(0);
+      for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
+        ok = mbar_wait(kv_full + 8 * (j % kUStages), (j / kUStages) & 1);
+        if (ok) {
+          tcgen05_fence_after();
+          issue_qk(j);
+        }
       }
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (!mbar_wait(p_full, j & 1)) { ok = false; break; }
+        if (!mbar_wait(p_full + 8 * (j & 1), (j >> 1) & 1)) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t st = ring_s + (j % kUStages) * kUStage + 2 * kKVSlab;      // V of this tile
+        const uint32_t pa = tmem + kColS + (j & 1) * 64;                           // P hi, then P lo
 #pragma unroll
         for (int half = 0; half < 2; ++half)
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t da = umma_desc_sw128(p_s + half * kPSlab + kk * 32, 0, 1024);
             const uint64_t db = umma_desc_sw128(st + kk * 16 * 128, /*next 64 dims*/ kKVSlab, /*next 8 tokens*/ 1024);
-            umma_bf16(tmem + kColO, da, db, idesc_pv, j > 0 || half > 0 || kk > 0);
+            umma_bf16_ts(tmem + kColO, pa + half * 32 + kk * 8, db, idesc_pv, j > 0 || half > 0 || kk > 0);
           }
         umma_commit(kv_empty + 8 * (j % kUStages));       // the stage may be refilled ...
-        umma_commit(o_full);                              // ... and P / O belong to the softmax warps again
-        if (j + 1 < n_tiles) {
-          const int s1 = (j + 1) % kUStages;
-          if (!mbar_wait(kv_full + 8 * s1, ((j + 1) / kUStages) & 1)) { ok = false; break; }
+        umma_commit(o_full);                              // ... and O is quiescent until the next P.V
+        if (j + 2 < n_tiles) {                            // S of tile j + 2 reuses this tile's buffer (after its P.V, in order)
+          const int s2 = (j + 2) % kUStages;
+          if (!mbar_wait(kv_full + 8 * s2, ((j + 2) / kUStages) & 1)) { ok = false; break; }
           tcgen05_fence_after();
-          issue_qk(j + 1);
+          issue_qk(j + 2);
         }
       }
       if (!ok) failed = 1;
@@ -184,13 +188,14 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_umma_kernel(PrefillParam
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      if (!__all_sync(0xffffffffu, mbar_wait(s_full, j & 1))) { ok = false; break; }   // warp-uniform: tcgen05.ld follows
+      const uint32_t sp = lane_addr + kColS + (j & 1) * 64;   // this tile's S / P buffer
+      if (!__all_sync(0xffffffffu, mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1))) { ok = false; break; }   // warp-uniform: tcgen05.ld follows
       tcgen05_fence_after();
       float x[kUN];
 #pragma unroll
       for (int c0 = 0; c0 < kUN; c0 += 32) {
         uint32_t v[32];
-        tmem_ld_32x32b_x32(lane_addr + kColS + c0, v);
+        tmem_ld_32x32b_x32(sp + c0, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) x[c0 + i] = __uint_as_float(v[i]) * sl2;
@@ -203,10 +208,6 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_umma_kernel(PrefillParam
       }
 #pragma unroll
       for (int i = 0; i < kUN; ++i) mx = fmaxf(mx, x[i]);
-      // P of the previous tile must have been consumed before it is overwritten, and O must be
-      // quiescent before it is rescaled: both are what o_full of the previous tile says.
-      if (j > 0 && !__all_sync(0xffffffffu, mbar_wait(o_full, (j - 1) & 1))) { ok = false; break; }
-      tcgen05_fence_after();
       // tcgen05.ld / .st are warp-wide instructions: the decision to rescale is taken per warp,
       // every lane then moves its reference to max(old, tile) (a factor of 1 where nothing changed).
       if (__any_sync(0xffffffffu, mx > m_ref + kRescaleGap || (m_ref == -INFINITY && mx != -INFINITY))) {
@@ -214,6 +215,9 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_umma_kernel(PrefillParam
         const float f = m_ref == -INFINITY ? 1.f : exp2f(m_ref - m_new);      // O is still empty while m_ref is -inf
         l *= f;
         if (j > 0) {
+          // O must be quiescent: P.V of the previous tile done (P.V of this one waits for this thread's P)
+          if (!__all_sync(0xffffffffu, mbar_wait(o_full, (j - 1) & 1))) { ok = false; break; }
+          tcgen05_fence_after();
 #pragma unroll
           for (int c0 = 0; c0 < kHeadDim; c0 += 32) {
             uint32_t v[32];
@@ -236,23 +240,22 @@ __global__ void __launch_bounds__(kUThreads, 1) prefill_umma_kernel(PrefillParam
         for (int r = (kv_end - t0) + (row >> 4); r < kUN; r += 8)
           *reinterpret_cast<uint4 *>(vst + ((row >> 3) & 1) * kKVSlab + r * 128 + (row & 7) * 16) = make_uint4(0, 0, 0, 0);
       }
+      {                                                     // P hi -> columns [0, 32), P lo -> [32, 64) of the buffer
+        uint32_t hi[32], lo[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {                         // 8 tokens per 16-byte chunk
-        uint32_t hi[4], lo[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = exp2f(x[c * 8 + 2 * e] - ref), p1 = exp2f(x[c * 8 + 2 * e + 1] - ref);
+        for (int i = 0; i < 32; ++i) {
+          const float p0 = exp2f(x[2 * i] - ref), p1 = exp2f(x[2 * i + 1] - ref);
           l += p0 + p1;
-          hi[e] = pack_bf16x2(p0, p1);
-          lo[e] = pack_bf16x2(p0 - bf16_lo(hi[e]), p1 - bf16_hi(hi[e]));
+          hi[i] = pack_bf16x2(p0, p1);
+          lo[i] = pack_bf16x2(p0 - bf16_lo(hi[i]), p1 - bf16_hi(hi[i]));
         }
-        const uint32_t off = sw128_offset(row, c);
-        *reinterpret_cast<uint4 *>(p_g + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        *reinterpret_cast<uint4 *>(p_g + kPSlab + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+        tmem_st_32x32b_x32(sp, hi);
+        tmem_st_32x32b_x32(sp + 32, lo);
+        tmem_st_wait();
       }
-      fence_proxy_async_smem();
+      fence_proxy_async_smem();        // the cleared V rows of a ragged tile
       tcgen05_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive(p_full + 8 * (j & 1));
     }
     if (ok && !__all_sync(0xffffffffu, mbar_wait(o_full, (n_tiles - 1) & 1))) ok = false;
     tcgen05_fence_after();

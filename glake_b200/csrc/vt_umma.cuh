@@ -88,6 +88,17 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       "}" ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
       : "memory");
 }
+// Same with A taken from tensor memory (K-major by construction): lane = row, two
+// consecutive k of a 16-bit type per 32-bit column, so a K = 16 step spans 8 columns.
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n"
+      " .reg .pred p;\n"
+      " setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+      "}" ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+      : "memory");
+}
 // Makes the mbarrier at `bar` (shared-memory address) receive one arrival when all MMAs
 // issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {

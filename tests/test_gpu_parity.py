@@ -16,7 +16,7 @@ from tests import synth
 from tests.test_oracle import SCALE, load_golden
 
 pytestmark = pytest.mark.gpu
-UMMA = os.environ.get("VT_PREFILL_ENGINE", "").startswith("u")   # tcgen05 prefill kernel selected
+UMMA = not os.environ.get("VT_PREFILL_ENGINE", "").startswith("m")   # with tensor maps: tcgen05 kernel unless mma.sync is forced
 
 
 def close_2e3(a, b, ulp_slack=False):
@@ -429,6 +429,35 @@ def test_prefill_long_prompts_both_copy_paths(G, oracle, h, kvh):
             outs.append(out)
         if not UMMA:
             assert torch.equal(outs[0], outs[1])
+    finally:
+        kv.close()
+
+
+@pytest.mark.parametrize("h,kvh,scale", [(4, 4, 1.0), (8, 1, 0.6), (16, 2, SCALE)])
+def test_prefill_tensor_core_path_rescales_and_edges(G, oracle, h, kvh, scale):
+    """The tcgen05 prefill kernel where its own machinery matters: logits large enough
+    that row maxima jump by more than 2^8 between tiles (the O rows in tensor memory are
+    rescaled), a single tile, a one-token extension of a long prefix, query counts that
+    are no multiple of 128, an entry with nothing to do."""
+    from glake_b200 import ops
+    lens = [40, 129, 777, 1500, 300]
+    q_lens = [40, 129, 1, 700, 0]
+    _, k, v = synth.make_case(1200 + h, lens, h, kvh)
+    rs = np.random.RandomState(10)
+    kv = G.GpuKV(k, v, kvh)
+    try:
+        starts = np.concatenate([[0], np.cumsum(q_lens)[:-1]]).astype(np.int32)
+        q = synth.normal_bf16(rs, int(sum(q_lens)), h, 128)
+        ql, qs = torch.tensor(q_lens, dtype=torch.int32), torch.from_numpy(starts)
+        r = oracle.fill_ranges(k, v)
+        port = oracle.port_prefill_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32), ql, qs,
+                                        kvh, scale)
+        out = torch.zeros_like(q, device="cuda")
+        ops.prefill_attention(out, q.cuda(), kv.k_table, kv.v_table, kvh, scale, kv.meta.slot_mapping,
+                              kv.meta.seq_lens_tensor, ql.cuda(), qs.cuda(), max(q_lens), maps=kv.engine.prefill_maps(0))
+        torch.cuda.synchronize()
+        ok, err = close_2e3(out.cpu(), port, ulp_slack=True)
+        assert ok, err
     finally:
         kv.close()
 
