@@ -19,7 +19,7 @@
 //              columns [128, 256); tcgen05.commit signals the mbarriers the others wait on.
 // Hand-offs (mbarriers, every wait bounded): kv_full / kv_empty per ring stage,
 // s_full / p_full per S/P buffer (S ready; P written, 128 arrivals), o_full (P.V of
-// a tile done: O may be rescaled or read).
+// a tile done: O may be rescaled), o_last (all of O done).
 // Shared memory: Q 32 KB + ring 2 x 32 KB = 96 KB and 256 TMEM columns: two CTAs per SM.
 #include "../../include/vtensor.h"
 #include "vt_device.cuh"
@@ -60,7 +60,7 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
   unsigned char *q_g = sm, *ring_g = sm + 2 * kQSlab;
   uint64_t *bars = reinterpret_cast<uint64_t *>(ring_g + kUStages * kUStage);
   const uint32_t kv_full = smem_u32(bars), kv_empty = kv_full + 8 * kUStages, s_full = kv_empty + 8 * kUStages,
-                 p_full = s_full + 16, o_full = p_full + 16, q_full = o_full + 8;
+                 p_full = s_full + 16, o_full = p_full + 16, q_full = o_full + 8, o_last = q_full + 8;
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
@@ -84,6 +84,7 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
       mbar_init(p_full + 8 * bf, kUM);
     }
     mbar_init(o_full, 1);
+    mbar_init(o_last, 1);
     mbar_init(q_full, kUM);
     mbar_fence_init();
     failed = 0;
@@ -157,6 +158,7 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
           }
         umma_commit(kv_empty + 8 * (j % kUStages));       // the stage may be refilled ...
         umma_commit(o_full);                              // ... and O is quiescent until the next P.V
+        if (j == n_tiles - 1) umma_commit(o_last);
         if (j + 2 < n_tiles) {                            // S of tile j + 2 reuses this tile's buffer (after its P.V, in order)
           const int s2 = (j + 2) % kUStages;
           if (!mbar_wait(kv_full + 8 * s2, ((j + 2) / kUStages) & 1)) { ok = false; break; }
@@ -257,7 +259,9 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
       tcgen05_fence_before();
       mbar_arrive(p_full + 8 * (j & 1));
     }
-    if (ok && !__all_sync(0xffffffffu, mbar_wait(o_full, (n_tiles - 1) & 1))) ok = false;
+    // Not o_full: these threads do not follow its phases tile by tile, and a parity wait can only
+    // tell the latest completed phase from the one before it.  o_last completes exactly once.
+    if (ok && !__all_sync(0xffffffffu, mbar_wait(o_last, 0))) ok = false;
     tcgen05_fence_after();
     if (__all_sync(0xffffffffu, ok)) {                      // warp-wide TMEM loads; only the stores are per row
       const float inv = l > 0.f ? 1.f / l : 0.f;

@@ -462,6 +462,45 @@ def test_prefill_tensor_core_path_rescales_and_edges(G, oracle, h, kvh, scale):
         kv.close()
 
 
+def test_prefill_full_size_engines_agree_and_normalise(G):
+    """4096-token prompts, 32 q heads over 8 kv heads (two CTAs per SM, 64 K/V tiles per CTA):
+    the tcgen05 kernel (tensor maps) and the mma.sync kernel (row copies) are independent
+    implementations of the same fp32 softmax and must agree to 2e-3 (or one bf16 ulp where the
+    output is O(1)); with V = 1 every output
+    must be exactly 1 (each visible token counted once, sums and rescales consistent)."""
+    from glake_b200 import ops
+    from glake_b200.backend import VTensorCacheEngine, VTensorMetadata, prepare_step
+    b, h, kvh, n = 2, 32, 8, 4096
+    gen = torch.Generator(device="cuda").manual_seed(5)
+    eng = VTensorCacheEngine(1, kvh, 128, b, n + 8)
+    try:
+        meta = VTensorMetadata(list(range(b)), [n] * b, kvh, 128, num_prefills=b)
+        prepare_step(meta, eng)
+        k = torch.randn(b * n, kvh, 128, device="cuda", generator=gen).bfloat16()
+        q = torch.randn(b * n, h, 128, device="cuda", generator=gen).bfloat16()
+        ql = torch.full((b,), n, dtype=torch.int32, device="cuda")
+        qs = torch.arange(b, dtype=torch.int32, device="cuda") * n
+        kt, vt = eng.gpu_cache[0][0].vmm_ptr, eng.gpu_cache[0][1].vmm_ptr
+        for ones in (False, True):
+            v = torch.ones_like(k) if ones else torch.randn(b * n, kvh, 128, device="cuda", generator=gen).bfloat16()
+            ops.reshape_and_cache(k, v, eng.k_cache_ptr[0], eng.v_cache_ptr[0], meta.slot_m, meta.slot_mapping,
+                                  meta.seq_lens_tensor, meta.cache_seq_lens, n, kvh, 128)
+            outs = []
+            for maps in (None, eng.prefill_maps(0)):
+                out = torch.zeros_like(q)
+                ops.prefill_attention(out, q, kt, vt, kvh, SCALE, meta.slot_mapping, meta.seq_lens_tensor, ql, qs, n, maps=maps)
+                torch.cuda.synchronize()
+                outs.append(out)
+            if ones:
+                assert bool((outs[0] == 1).all()) and bool((outs[1] == 1).all())
+            else:
+                ok, err = close_2e3(outs[0], outs[1], ulp_slack=True)   # first rows attend few tokens: outputs of O(1)
+                assert ok, err
+                assert float(outs[1].float().abs().max()) > 0.05       # not trivially zero
+    finally:
+        eng.close()
+
+
 @pytest.mark.parametrize("seed", range(12))
 def test_flat_schedule_random_batches(G, oracle, seed):
     """Randomised batches for the persistent flat schedule: piece boundaries, stream
