@@ -79,7 +79,8 @@ __global__ void __maxnreg__(128) prefill_attn_kernel(PrefillParams p) {
   uint64_t *bars = reinterpret_cast<uint64_t *>(ring + kStages * kStage);
   const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + kStages);
 
-  const int qt = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+  // later query tiles see more context: they are scheduled first so that the short ones fill the tail
+  const int qt = gridDim.x - 1 - blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
   const int q_len = p.q_lens[b], seq_len = p.seq_lens[b];
   const int j0 = qt * kBM;
   if (j0 >= q_len) return;
@@ -343,7 +344,8 @@ int launch_prefill_attn(const PrefillParams &p, int max_q_len, cudaStream_t stre
       const char *e = getenv("VT_PREFILL_ENGINE");
       return e && e[0] == 'm';
     }();
-    const bool umma_ok = p.kvh * 64 <= 8192 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 && p.out_stride % 8 == 0;
+    const bool umma_ok = p.kvh * 64 <= 8192 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 && p.out_stride % 8 == 0 &&
+                         p.scale > 0.f;
     if (!legacy && umma_ok) return launch_prefill_umma(p, max_q_len, stream);
     // mma.sync with tensor copies: 64-row query tiles, three CTAs per SM (250 TFLOP/s causal at 4k prompts, 213 at 1k).
     return launch_cfg<PfCfg<4, 32, 3, true>>(p, max_q_len, stream);

@@ -47,6 +47,11 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *map, int x
       ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
+__device__ __forceinline__ float ex2_approx(float x) {      // 2^x, one MUFU op; -inf -> 0
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t *>(&v);
@@ -64,7 +69,8 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
-  const int qt = blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
+  // later query tiles see more context: they are scheduled first so that the short ones fill the tail
+  const int qt = gridDim.x - 1 - blockIdx.x, hq = blockIdx.y, b = blockIdx.z;
   const int q_len = p.q_lens[b], seq_len = p.seq_lens[b];
   const int j0 = qt * kUM;
   if (j0 >= q_len) return;                                  // whole CTA: nothing allocated yet
@@ -200,7 +206,7 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
         tmem_ld_32x32b_x32(sp + c0, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) x[c0 + i] = __uint_as_float(v[i]) * sl2;
+        for (int i = 0; i < 32; ++i) x[c0 + i] = __uint_as_float(v[i]);      // raw logits; the scale rides in the exponent's FMA
       }
       const int t0 = j * kUN;
       float mx = -INFINITY;
@@ -210,6 +216,7 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
       }
 #pragma unroll
       for (int i = 0; i < kUN; ++i) mx = fmaxf(mx, x[i]);
+      mx *= sl2;                                            // scale > 0 (checked by the launcher): max commutes with it
       // tcgen05.ld / .st are warp-wide instructions: the decision to rescale is taken per warp,
       // every lane then moves its reference to max(old, tile) (a factor of 1 where nothing changed).
       if (__any_sync(0xffffffffu, mx > m_ref + kRescaleGap || (m_ref == -INFINITY && mx != -INFINITY))) {
@@ -246,7 +253,7 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
         uint32_t hi[32], lo[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float p0 = exp2f(x[2 * i] - ref), p1 = exp2f(x[2 * i + 1] - ref);
+          const float p0 = ex2_approx(fmaf(x[2 * i], sl2, -ref)), p1 = ex2_approx(fmaf(x[2 * i + 1], sl2, -ref));
           l += p0 + p1;
           hi[i] = pack_bf16x2(p0, p1);
           lo[i] = pack_bf16x2(p0 - bf16_lo(hi[i]), p1 - bf16_hi(hi[i]));
