@@ -277,8 +277,10 @@ int vt_prefill_attn(void *out, int64_t out_stride, const void *q, int64_t q_stri
                     int max_q_len, float scale, int kv_dtype, uint32_t *status, void *stream);
 
 /* vt_prefill_attn with the K/V tiles fetched by TMA tensor copies (one request
- * per 32 tokens x 64 dims instead of one per token row), which lifts the
- * copy-request limit the row-copy version runs into.  Same arguments plus
+ * per 32 tokens x 64 dims instead of one per token row) and, when the shapes allow
+ * (kvh <= 128, out rows 16-byte aligned, scale > 0), the math on tcgen05.mma with
+ * the accumulators in tensor memory; otherwise on mma.sync.  Same results within
+ * the tolerance of vt_prefill_attn.  Same arguments plus
  *   maps   device copy of the table vt_prefill_maps_encode filled: for every slot
  *          id a K and a V tensor map (2 x 128 bytes per slot, 64-byte aligned).
  * vt_prefill_maps_encode writes that table into HOST memory (n_slots x 256 bytes,
