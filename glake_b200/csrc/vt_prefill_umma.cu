@@ -52,6 +52,28 @@ __device__ __forceinline__ float ex2_approx(float x) {      // 2^x, one MUFU op;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Two fp32 lanes per instruction (sm_100 packed fp32 math): halves the FMA / ADD count of the softmax.
+__device__ __forceinline__ uint64_t f2_pack(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float &a, float &b) { asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t *>(&v);
@@ -200,13 +222,16 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
       if (!__all_sync(0xffffffffu, mbar_wait(s_full + 8 * (j & 1), (j >> 1) & 1))) { ok = false; break; }   // warp-uniform: tcgen05.ld follows
       tcgen05_fence_after();
       float x[kUN];
-#pragma unroll
-      for (int c0 = 0; c0 < kUN; c0 += 32) {
-        uint32_t v[32];
-        tmem_ld_32x32b_x32(sp + c0, v);
+      {                                                     // both halves of the row in flight before the one wait
+        uint32_t v0[32], v1[32];
+        tmem_ld_32x32b_x32(sp, v0);
+        tmem_ld_32x32b_x32(sp + 32, v1);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) x[c0 + i] = __uint_as_float(v[i]);      // raw logits; the scale rides in the exponent's FMA
+        for (int i = 0; i < 32; ++i) {                      // raw logits; the scale rides in the exponent's FMA
+          x[i] = __uint_as_float(v0[i]);
+          x[32 + i] = __uint_as_float(v1[i]);
+        }
       }
       const int t0 = j * kUN;
       float mx = -INFINITY;
@@ -215,7 +240,7 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
         for (int i = 0; i < kUN; ++i) x[i] = (t0 + i <= lim) ? x[i] : -INFINITY;
       }
 #pragma unroll
-      for (int i = 0; i < kUN; ++i) mx = fmaxf(mx, x[i]);
+      for (int i = 0; i < kUN; i += 2) mx = max3(mx, x[i], x[i + 1]);
       mx *= sl2;                                            // scale > 0 (checked by the launcher): max commutes with it
       // tcgen05.ld / .st are warp-wide instructions: the decision to rescale is taken per warp,
       // every lane then moves its reference to max(old, tile) (a factor of 1 where nothing changed).
@@ -251,12 +276,24 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
       }
       {                                                     // P hi -> columns [0, 32), P lo -> [32, 64) of the buffer
         uint32_t hi[32], lo[32];
+        const uint64_t sl2_2 = f2_pack(sl2, sl2), nref2 = f2_pack(-ref, -ref), minus1 = f2_pack(-1.f, -1.f);
+        uint64_t l2 = f2_pack(l, 0.f);
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          const float p0 = ex2_approx(fmaf(x[2 * i], sl2, -ref)), p1 = ex2_approx(fmaf(x[2 * i + 1], sl2, -ref));
-          l += p0 + p1;
+          float a0, a1;
+          f2_unpack(f2_fma(f2_pack(x[2 * i], x[2 * i + 1]), sl2_2, nref2), a0, a1);
+          const float p0 = ex2_approx(a0), p1 = ex2_approx(a1);
+          const uint64_t p2 = f2_pack(p0, p1);
+          l2 = f2_add(l2, p2);
           hi[i] = pack_bf16x2(p0, p1);
-          lo[i] = pack_bf16x2(p0 - bf16_lo(hi[i]), p1 - bf16_hi(hi[i]));
+          float r0, r1;
+          f2_unpack(f2_fma(f2_pack(bf16_lo(hi[i]), bf16_hi(hi[i])), minus1, p2), r0, r1);   // p - hi, exact
+          lo[i] = pack_bf16x2(r0, r1);
+        }
+        {
+          float la, lb;
+          f2_unpack(l2, la, lb);
+          l = la + lb;
         }
         tmem_st_32x32b_x32(sp, hi);
         tmem_st_32x32b_x32(sp + 32, lo);
