@@ -17,7 +17,8 @@
 //              softmax warps work on tile j; O += P_hi.V + P_lo.V (2 x 4 steps, N = 128,
 //              P read from TMEM as the A operand, V as the MN-major B operand) into
 //              columns [128, 256); tcgen05.commit signals the mbarriers the others wait on.
-// Hand-offs (mbarriers, every wait bounded): kv_full / kv_empty per ring stage,
+// Hand-offs (mbarriers, every wait bounded): k/v_full and k/v_empty per ring stage
+// (the K slot is released after Q.K^T, the V slot after P.V),
 // s_full / p_full per S/P buffer (S ready; P written, 128 arrivals), o_full (P.V of
 // a tile done: O may be rescaled), o_last (all of O done).
 // Shared memory: Q 32 KB + ring 2 x 32 KB = 96 KB and 256 TMEM columns: two CTAs per SM.
@@ -86,8 +87,11 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
   const uint32_t q_s = base, ring_s = q_s + 2 * kQSlab;
   unsigned char *q_g = sm, *ring_g = sm + 2 * kQSlab;
   uint64_t *bars = reinterpret_cast<uint64_t *>(ring_g + kUStages * kUStage);
-  const uint32_t kv_full = smem_u32(bars), kv_empty = kv_full + 8 * kUStages, s_full = kv_empty + 8 * kUStages,
-                 p_full = s_full + 16, o_full = p_full + 16, q_full = o_full + 8, o_last = q_full + 8;
+  // K and V slots of a stage are handed over separately: the K slot is free as soon as Q.K^T of its
+  // tile is done, long before P.V releases the V slot, so K of tile j + 2 is fetched ~1.5 tiles ahead.
+  const uint32_t k_full = smem_u32(bars), v_full = k_full + 8 * kUStages, k_empty = v_full + 8 * kUStages,
+                 v_empty = k_empty + 8 * kUStages, s_full = v_empty + 8 * kUStages, p_full = s_full + 16,
+                 o_full = p_full + 16, q_full = o_full + 8, o_last = q_full + 8;
   __shared__ uint32_t tmem_slot;
   __shared__ int failed;
 
@@ -104,8 +108,10 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
 
   if (tid == 0) {
     for (int s = 0; s < kUStages; ++s) {
-      mbar_init(kv_full + 8 * s, 1);
-      mbar_init(kv_empty + 8 * s, 1);
+      mbar_init(k_full + 8 * s, 1);
+      mbar_init(v_full + 8 * s, 1);
+      mbar_init(k_empty + 8 * s, 1);
+      mbar_init(v_empty + 8 * s, 1);
     }
     for (int bf = 0; bf < 2; ++bf) {
       mbar_init(s_full + 8 * bf, 1);
@@ -131,22 +137,29 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
     if (lane == 0) {
       const int64_t slot = p.slot_ids[b];
       const char *maps = static_cast<const char *>(p.maps) + static_cast<size_t>(slot) * 256;
-      for (int j = 0; j < n_tiles; ++j) {
+      // kv = 0: K of tile j, kv = 1: V of tile j (second 32-token box only if it holds context)
+      auto load = [&](int j, int kv) -> bool {
         const int s = j % kUStages;
-        if (j >= kUStages && !mbar_wait(kv_empty + 8 * s, ((j / kUStages) - 1) & 1)) { failed = 1; break; }
+        if (j >= kUStages && !mbar_wait((kv ? v_empty : k_empty) + 8 * s, ((j / kUStages) - 1) & 1)) return false;
         const int t0 = j * kUN;
-        const int boxes = (kv_end - t0 > 32) ? 2 : 1;       // the second 32-token box only if it holds context
-        const uint32_t dst = ring_s + s * kUStage, bar = kv_full + 8 * s;
-        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(boxes) * 4u * 4096u);
+        const int boxes = (kv_end - t0 > 32) ? 2 : 1;
+        const uint32_t dst = ring_s + s * kUStage + kv * 2 * kKVSlab, bar = (kv ? v_full : k_full) + 8 * s;
+        const char *map = maps + kv * 128;
+        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(boxes) * 2u * 4096u);
         for (int bx = 0; bx < boxes; ++bx) {
-          const int z = t0 + 32 * bx;
-          const uint32_t d = dst + bx * 4096;
-          tma_load_3d(d, maps, 0, kv_head, z, bar);
-          tma_load_3d(d + kKVSlab, maps, 64, kv_head, z, bar);
-          tma_load_3d(d + 2 * kKVSlab, maps + 128, 0, kv_head, z, bar);
-          tma_load_3d(d + 3 * kKVSlab, maps + 128, 64, kv_head, z, bar);
+          tma_load_3d(dst + bx * 4096, map, 0, kv_head, t0 + 32 * bx, bar);
+          tma_load_3d(dst + bx * 4096 + kKVSlab, map, 64, kv_head, t0 + 32 * bx, bar);
         }
+        return true;
+      };
+      // Issue order = the order in which the MMAs free the slots: K(j+1) after Q.K^T(j-1), V(j) after P.V(j-2), ...
+      bool ok = load(0, 0);
+      if (ok && n_tiles > 1) ok = load(1, 0);
+      for (int j = 0; ok && j < n_tiles; ++j) {
+        ok = load(j, 1);
+        if (ok && j + 2 < n_tiles) ok = load(j + 2, 0);
       }
+      if (!ok) failed = 1;
     }
   } else if (warp == 5) {
     // ---------------- MMA issuer ----------------
@@ -163,17 +176,21 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
           const uint64_t db = umma_desc_sw128(st + (kk >> 2) * kKVSlab + (kk & 3) * 32, 0, 1024);
           umma_bf16(tmem + kColS + (j & 1) * 64, da, db, idesc_qk, kk > 0);
         }
+        umma_commit(k_empty + 8 * (j % kUStages));         // the K slot may be refilled
         umma_commit(s_full + 8 * (j & 1));
       };
       for (int j = 0; ok && j < 2 && j < n_tiles; ++j) {
-        ok = mbar_wait(kv_full + 8 * (j % kUStages), (j / kUStages) & 1);
+        ok = mbar_wait(k_full + 8 * (j % kUStages), (j / kUStages) & 1);
         if (ok) {
           tcgen05_fence_after();
           issue_qk(j);
         }
       }
       for (int j = 0; ok && j < n_tiles; ++j) {
-        if (!mbar_wait(p_full + 8 * (j & 1), (j >> 1) & 1)) { ok = false; break; }
+        if (!mbar_wait(v_full + 8 * (j % kUStages), (j / kUStages) & 1) || !mbar_wait(p_full + 8 * (j & 1), (j >> 1) & 1)) {
+          ok = false;
+          break;
+        }
         tcgen05_fence_after();
         const uint32_t st = ring_s + (j % kUStages) * kUStage + 2 * kKVSlab;      // V of this tile
         const uint32_t pa = tmem + kColS + (j & 1) * 64;                           // P hi, then P lo
@@ -184,12 +201,12 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
             const uint64_t db = umma_desc_sw128(st + kk * 16 * 128, /*next 64 dims*/ kKVSlab, /*next 8 tokens*/ 1024);
             umma_bf16_ts(tmem + kColO, pa + half * 32 + kk * 8, db, idesc_pv, j > 0 || half > 0 || kk > 0);
           }
-        umma_commit(kv_empty + 8 * (j % kUStages));       // the stage may be refilled ...
+        umma_commit(v_empty + 8 * (j % kUStages));        // the V slot may be refilled ...
         umma_commit(o_full);                              // ... and O is quiescent until the next P.V
         if (j == n_tiles - 1) umma_commit(o_last);
         if (j + 2 < n_tiles) {                            // S of tile j + 2 reuses this tile's buffer (after its P.V, in order)
           const int s2 = (j + 2) % kUStages;
-          if (!mbar_wait(kv_full + 8 * s2, ((j + 2) / kUStages) & 1)) { ok = false; break; }
+          if (!mbar_wait(k_full + 8 * s2, ((j + 2) / kUStages) & 1)) { ok = false; break; }
           tcgen05_fence_after();
           issue_qk(j + 2);
         }
@@ -269,7 +286,7 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
       if (kv_end - t0 < kUN) {
         // Ragged last tile: V rows past the context may hold anything (0 * NaN = NaN).  The rows of
         // this thread's share are cleared in both 64-dim halves before the tensor core reads them.
-        if (!__all_sync(0xffffffffu, mbar_wait(kv_full + 8 * (j % kUStages), (j / kUStages) & 1))) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(v_full + 8 * (j % kUStages), (j / kUStages) & 1))) { ok = false; break; }
         unsigned char *vst = ring_g + (j % kUStages) * kUStage + 2 * kKVSlab;
         for (int r = (kv_end - t0) + (row >> 4); r < kUN; r += 8)
           *reinterpret_cast<uint4 *>(vst + ((row >> 3) & 1) * kKVSlab + r * 128 + (row & 7) * 16) = make_uint4(0, 0, 0, 0);
