@@ -462,6 +462,17 @@ def test_prefill_tensor_core_path_rescales_and_edges(G, oracle, h, kvh, scale):
         kv.close()
 
 
+def test_tcgen05_descriptor_probe():
+    """The one-tile probe behind vt_umma.cuh's descriptor encodings (K-major and MN-major
+    operands, 128-byte swizzle, TMEM accumulator) still matches its host reference."""
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "glake_b200", "csrc", "probe", "umma_tile")
+    if not os.path.isfile(exe):
+        pytest.skip("probe not built (make -C glake_b200/csrc probe)")
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0 and res.stdout.count("-> OK") == 3, res.stdout + res.stderr
+
+
 def test_prefill_full_size_engines_agree_and_normalise(G):
     """4096-token prompts, 32 q heads over 8 kv heads (two CTAs per SM, 64 K/V tiles per CTA):
     the tcgen05 kernel (tensor maps) and the mma.sync kernel (row copies) are independent
