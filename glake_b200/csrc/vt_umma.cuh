@@ -70,7 +70,9 @@ __host__ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr,
   return static_cast<uint64_t>((smem_addr & 0x3ffffu) >> 4) | (static_cast<uint64_t>((lbo >> 4) & 0x3fffu) << 16) |
          (static_cast<uint64_t>((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46) | (2ull << 61);
 }
-// Instruction descriptor for kind::f16 with bf16 operands and an fp32 accumulator:
+// Instruction descriptor for kind::f16 with bf16 operands and an fp32 accumulator (A and B
+// must have the same format: a half-precision A with a bf16 B is rejected by the hardware as an
+// illegal instruction):
 // accumulator format (bits 4-5) 1 = f32, A / B format (7-9, 10-12) 1 = bf16, A / B
 // major-ness (15, 16) 0 = K-major 1 = MN-major, N >> 3 (17-22), M >> 4 (24-28).
 __host__ __device__ __forceinline__ uint32_t umma_idesc_bf16_f32(int m, int n, bool a_mn, bool b_mn) {
