@@ -106,7 +106,30 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
   const int n_tiles = (kv_end + kUN - 1) / kUN;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-  if (tid == 0) {
+  // Set-up, overlapped: the producer lane initialises the barriers and at once starts the first K/V
+  // copies (nobody else touches a barrier before the CTA-wide sync), warp 5 allocates tensor memory,
+  // the softmax warps bring their Q rows into shared memory.
+  const int64_t slot = p.slot_ids[b];
+  const char *maps = static_cast<const char *>(p.maps) + static_cast<size_t>(slot) * 256;
+  // kv = 0: K of tile j, kv = 1: V of tile j (second 32-token box only if it holds context)
+  auto load = [&](int j, int kv) -> bool {
+    const int s = j % kUStages;
+    if (j >= kUStages && !mbar_wait((kv ? v_empty : k_empty) + 8 * s, ((j / kUStages) - 1) & 1)) return false;
+    const int t0 = j * kUN;
+    const int boxes = (kv_end - t0 > 32) ? 2 : 1;
+    const uint32_t dst = ring_s + s * kUStage + kv * 2 * kKVSlab, bar = (kv ? v_full : k_full) + 8 * s;
+    const char *map = maps + kv * 128;
+    mbar_arrive_expect_tx(bar, static_cast<uint32_t>(boxes) * 2u * 4096u);
+    for (int bx = 0; bx < boxes; ++bx) {
+      tma_load_3d(dst + bx * 4096, map, 0, kv_head, t0 + 32 * bx, bar);
+      tma_load_3d(dst + bx * 4096 + kKVSlab, map, 64, kv_head, t0 + 32 * bx, bar);
+    }
+    return true;
+  };
+  const int row = warp * 32 + lane;                         // softmax warps: row of the tile = TMEM lane
+  const int jrow = j0 + row;                                // entry-relative query index
+  const bool row_ok = jrow < q_len;
+  if (warp == 4 && lane == 0) {
     for (int s = 0; s < kUStages; ++s) {
       mbar_init(k_full + 8 * s, 1);
       mbar_init(v_full + 8 * s, 1);
@@ -122,10 +145,22 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
     mbar_init(q_full, kUM);
     mbar_fence_init();
     failed = 0;
-  }
-  if (warp == 5) {
+    load(0, 0);                                             // tiles 0 and 1 need no free slot
+    if (n_tiles > 1) load(1, 0);
+    load(0, 1);
+  } else if (warp == 5) {
     tmem_alloc(smem_u32(&tmem_slot), kTmemCols);
     tmem_relinquish();
+  } else if (warp < 4) {
+    // Q row -> shared memory (zeros beyond q_len), K-major 128-byte swizzle, two 64-dim slabs
+    const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.q) +
+                                                       (static_cast<int64_t>(p.q_start[b]) + jrow) * p.q_stride + hq * kHeadDim);
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const uint4 v = row_ok ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4 *>(q_g + (c >> 3) * kQSlab + sw128_offset(row, c & 7)) = v;
+    }
+    fence_proxy_async_smem();
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -135,28 +170,10 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
   if (warp == 4) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      const int64_t slot = p.slot_ids[b];
-      const char *maps = static_cast<const char *>(p.maps) + static_cast<size_t>(slot) * 256;
-      // kv = 0: K of tile j, kv = 1: V of tile j (second 32-token box only if it holds context)
-      auto load = [&](int j, int kv) -> bool {
-        const int s = j % kUStages;
-        if (j >= kUStages && !mbar_wait((kv ? v_empty : k_empty) + 8 * s, ((j / kUStages) - 1) & 1)) return false;
-        const int t0 = j * kUN;
-        const int boxes = (kv_end - t0 > 32) ? 2 : 1;
-        const uint32_t dst = ring_s + s * kUStage + kv * 2 * kKVSlab, bar = (kv ? v_full : k_full) + 8 * s;
-        const char *map = maps + kv * 128;
-        mbar_arrive_expect_tx(bar, static_cast<uint32_t>(boxes) * 2u * 4096u);
-        for (int bx = 0; bx < boxes; ++bx) {
-          tma_load_3d(dst + bx * 4096, map, 0, kv_head, t0 + 32 * bx, bar);
-          tma_load_3d(dst + bx * 4096 + kKVSlab, map, 64, kv_head, t0 + 32 * bx, bar);
-        }
-        return true;
-      };
       // Issue order = the order in which the MMAs free the slots: K(j+1) after Q.K^T(j-1), V(j) after P.V(j-2), ...
-      bool ok = load(0, 0);
-      if (ok && n_tiles > 1) ok = load(1, 0);
+      bool ok = true;
       for (int j = 0; ok && j < n_tiles; ++j) {
-        ok = load(j, 1);
+        if (j > 0) ok = load(j, 1);
         if (ok && j + 2 < n_tiles) ok = load(j + 2, 0);
       }
       if (!ok) failed = 1;
@@ -215,22 +232,9 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
     }
   } else {
     // ---------------- softmax warps: thread = query row ----------------
-    const int row = warp * 32 + lane;                       // row of the tile = TMEM lane
-    const int jrow = j0 + row;                              // entry-relative query index
-    const bool row_ok = jrow < q_len;
     const int lim = pos0 + row;                             // last visible token
     const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-    {  // Q row -> shared memory (zeros beyond q_len), K-major 128-byte swizzle, two 64-dim slabs
-      const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const __nv_bfloat16 *>(p.q) +
-                                                         (static_cast<int64_t>(p.q_start[b]) + jrow) * p.q_stride + hq * kHeadDim);
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        const uint4 v = row_ok ? __ldg(src + c) : make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4 *>(q_g + (c >> 3) * kQSlab + sw128_offset(row, c & 7)) = v;
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(q_full);
-    }
+    mbar_arrive(q_full);                                    // this row of Q was written (and fenced) before the sync
     const float sl2 = p.scale * 1.4426950408889634f;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
