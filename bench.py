@@ -417,6 +417,8 @@ def run_ours(args):
                      "peak_source": "measured (MEASURED_PEAKS.json hbm_gbs)" if "hbm_gbs" in peaks else "fallback"},
         "clocks": clocks,
     }
+    if world == 1:
+        line["prefill"] = prefill_probe(job, peaks)
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_baseline(name, args.seed, world)
     print(json.dumps(line), flush=True)
@@ -443,6 +445,63 @@ def load_traffic(name, algorithmic_bytes_per_launch):
 # ----------------------------------------------------------------------------
 # CPU baseline / reference arm: the reference's own CPU-backend kernels
 # ----------------------------------------------------------------------------
+def prefill_probe(job, peaks, prompts=2, tokens=4096, iters=10):
+    """Extra, outside the timed region and the metric: the prefill kernel of the same head
+    shape on a few prompts taken from the pool's free chunks (causal TFLOP/s, CUDA events)."""
+    try:
+        torch = job.torch
+        from glake_b200 import ops
+        from glake_b200.backend import VTensorCacheEngine, VTensorMetadata, prepare_step
+        if job.e != 2:
+            return {"skipped": "bf16 KV only"}
+        row = job.kvh * D * 2
+        need = prompts * 2 * ((tokens * row + (2 << 20) - 1) // (2 << 20)) + 8
+        if job.A.stats()["chunks_free"] < need:
+            return {"skipped": "not enough free chunks"}
+        eng = VTensorCacheEngine(1, job.kvh, D, prompts, tokens + 8)
+        try:
+            meta = VTensorMetadata(list(range(prompts)), [tokens] * prompts, job.kvh, D, num_prefills=prompts)
+            prepare_step(meta, eng)
+            g = torch.Generator(device="cuda").manual_seed(1)
+            k = torch.randn(prompts * tokens, job.kvh, D, device="cuda", generator=g).bfloat16()
+            v = torch.randn(prompts * tokens, job.kvh, D, device="cuda", generator=g).bfloat16()
+            q = torch.randn(prompts * tokens, job.h, D, device="cuda", generator=g).bfloat16()
+            ops.reshape_and_cache(k, v, eng.k_cache_ptr[0], eng.v_cache_ptr[0], meta.slot_m, meta.slot_mapping,
+                                  meta.seq_lens_tensor, meta.cache_seq_lens, tokens, job.kvh, D)
+            out = torch.empty_like(q)
+            ql = torch.full((prompts,), tokens, dtype=torch.int32, device="cuda")
+            qs = torch.arange(prompts, dtype=torch.int32, device="cuda") * tokens
+            kt, vt = eng.gpu_cache[0][0].vmm_ptr, eng.gpu_cache[0][1].vmm_ptr
+            maps = eng.prefill_maps(0)
+
+            def run():
+                ops.prefill_attention(out, q, kt, vt, job.kvh, D ** -0.5, meta.slot_mapping, meta.seq_lens_tensor, ql, qs,
+                                      tokens, maps=maps)
+            for _ in range(3):
+                run()
+            torch.cuda.synchronize()
+            a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                run()
+            z.record()
+            torch.cuda.synchronize()
+            ms = a.elapsed_time(z) / iters
+            tf = 2.0 * prompts * job.h * tokens * tokens * D / (ms * 1e-3) / 1e12
+            peak = float(peaks.get("bf16_tflops", 1590.0))
+            legacy = os.environ.get("VT_PREFILL_ENGINE", "").startswith("m")
+            return {"tflops_causal": round(tf, 1), "ms": round(ms, 4), "prompts": prompts, "tokens": tokens,
+                    "q_heads": job.h, "kv_heads": job.kvh,
+                    "kernel": "mma.sync" if (maps is None or legacy) else "tcgen05.mma, S/P/O in tensor memory, TMA tensor copies",
+                    "peak_tflops": peak, "frac_of_peak": round(tf / peak, 4),
+                    "note": "causal half of the flops only; P is applied as hi + lo bf16 halves, so the tensor cores "
+                            "execute about 1.5 x this; not part of the metric or the timed region"}
+        finally:
+            eng.close()
+    except Exception as exc:      # never let the extra take the bench line down
+        return {"error": f"{type(exc).__name__}: {exc}"[:200]}
+
+
 def cpu_sample(name, seed, world, budget_s=12.0, max_seqs=None):
     """Times the reference CPU attention (oracle/_ref; the C port if that cannot
     load) on ONE layer of the workload, all host threads.  Returns
