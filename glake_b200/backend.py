@@ -100,10 +100,12 @@ class VTensorMetadata:
     set_used_size: Optional[List[int]] = None
     extend_seq_list: List[int] = field(default_factory=list)
     kv_elem_size: int = 2
+    query_lens: Optional[List[int]] = None           # prefill: NEW tokens per entry (default: seq_lens, i.e. no prefix)
     # filled by prepare_step
     slot_mapping: Optional[torch.Tensor] = None      # int64 [B] slot ids (device)
     seq_lens_tensor: Optional[torch.Tensor] = None   # int32 [B] (device)
     cache_seq_lens: Optional[torch.Tensor] = None    # int32 [B] prefill source-row offsets
+    query_lens_tensor: Optional[torch.Tensor] = None # int32 [B] rows each entry appends (1 for decode)
     slot_m: Optional[torch.Tensor] = None            # int64 [B] destination byte offsets
     max_seq_len: int = 0
     k_cache_segment_ptr_list: Optional[list] = None
@@ -131,7 +133,7 @@ def prepare_step_host(meta: VTensorMetadata, engine: VTensorCacheEngine):
                 seg.eagerExtend(kv_size, slot_id)
         rows = [1] * len(slots)
     else:
-        rows = meta.query_lens if getattr(meta, "query_lens", None) else meta.seq_lens
+        rows = meta.query_lens if meta.query_lens else meta.seq_lens
         kv_size_list = [n * kv_size for n in rows]
     set_used = meta.set_used_size if meta.set_used_size is not None else [0] * len(slots)
     slot_m = vmmAllocator.extend_kv_cache_batch(None, None, slots, kv_size_list, segs, set_used, kv_size, decode)
@@ -140,6 +142,8 @@ def prepare_step_host(meta: VTensorMetadata, engine: VTensorCacheEngine):
         starts.append(acc)
         acc += r
     meta.max_seq_len = max(meta.seq_lens) if meta.seq_lens else 0
+    meta.max_query_len = max(rows) if rows else 0
+    meta._rows = list(rows)
     return slot_m, starts
 
 
@@ -150,17 +154,20 @@ def prepare_step(meta: VTensorMetadata, engine: VTensorCacheEngine, device=None)
     slot_m, starts = prepare_step_host(meta, engine)
     slots = meta.slot_mapping_list
     n = len(slots)
-    host = torch.tensor(slot_m + list(slots) + list(meta.seq_lens) + starts, dtype=torch.int64).pin_memory()
+    host = torch.tensor(slot_m + list(slots) + list(meta.seq_lens) + starts + meta._rows, dtype=torch.int64).pin_memory()
     dev = host.to(device, non_blocking=True)
     meta.slot_m = dev[:n]
     meta.slot_mapping = dev[n:2 * n]
     meta.seq_lens_tensor = dev[2 * n:3 * n].to(torch.int32)
     meta.cache_seq_lens = dev[3 * n:4 * n].to(torch.int32)
+    meta.query_lens_tensor = dev[4 * n:5 * n].to(torch.int32)
     return meta
 
 
 class VTensorAttentionImpl:
-    """Decode branch of the reference's ``XFormersImpl`` on the vTensor layout."""
+    """The reference's ``XFormersImpl`` on the vTensor layout: the decode branch
+    (xformers.py:389-433) as one fused launch, and the prompt / prefix-extend branch
+    (xformers.py:310-388) as multi-row append + causal attention over the range."""
 
     def __init__(self, num_heads, head_size, scale, num_kv_heads=None, kv_cache_dtype="auto"):
         self.num_heads, self.head_size, self.scale = num_heads, head_size, float(scale)
@@ -171,14 +178,28 @@ class VTensorAttentionImpl:
             raise ValueError("head size 128 only")
 
     def forward(self, query, key, value, key_cache: KV_cache, value_cache: KV_cache, attn_metadata: VTensorMetadata,
-                kv_scale: float = 1.0, k_scale=None, v_scale=None):
-        """query ``[tokens, H*D]``, key/value ``[tokens, KVH*D]`` -> ``[tokens, H*D]``."""
+                kv_scale: float = 1.0, k_scale=None, v_scale=None, prefill_maps=None):
+        """query ``[tokens, H*D]``, key/value ``[tokens, KVH*D]`` -> ``[tokens, H*D]``.
+        ``prefill_maps``: the layer's tensor-map table (``VTensorCacheEngine.prefill_maps``),
+        used by the prompt branch when given."""
         query = query.view(-1, self.num_heads, self.head_size)
         key = key.view(-1, self.num_kv_heads, self.head_size)
         value = value.view(-1, self.num_kv_heads, self.head_size)
         m = attn_metadata
         if m.num_prefills > 0:
-            raise NotImplementedError("prefill goes through glake_b200.prefill")
+            if self.kv_cache_dtype not in ("auto", "bf16", "bfloat16", None):
+                raise NotImplementedError("prompt attention over an fp8 cache is not implemented")
+            layer = key_cache.layer_index
+            # the new rows go into the ranges first (entry i: query_lens[i] rows from source row
+            # cache_seq_lens[i]), then the new tokens attend over prefix + new tokens
+            ops.reshape_and_cache(key, value, m.k_cache_segment_ptr_list[layer], m.v_cache_segment_ptr_list[layer],
+                                  m.slot_m, m.slot_mapping, m.query_lens_tensor, m.cache_seq_lens,
+                                  max(m.max_query_len, 2), self.num_kv_heads, self.head_size)
+            output = torch.empty_like(query)
+            ops.prefill_attention(output, query, key_cache.vmm_ptr, value_cache.vmm_ptr, self.num_kv_heads, self.scale,
+                                  m.slot_mapping, m.seq_lens_tensor, m.query_lens_tensor, m.cache_seq_lens,
+                                  m.max_query_len, maps=prefill_maps)
+            return output.view(-1, self.num_heads * self.head_size)
         # append + attention of the layer as one fused step (one kernel launch for a
         # bf16 cache); equivalent to ops.reshape_and_cache followed by ops.fwd_kvcache
         output = torch.empty_like(query)

@@ -290,6 +290,52 @@ def test_backend_forward_decode_steps(G, oracle):
         eng.close()
 
 
+@pytest.mark.parametrize("use_maps", [False, True])
+def test_backend_forward_prompt_extend_decode(G, oracle, use_maps):
+    """The backend binding through a request's life: prompts, a prefix-extend chunk
+    (new tokens appended behind the cached prefix and attending over prefix + new),
+    then decode steps; two layers; every output against the oracle."""
+    from glake_b200.backend import VTensorAttentionImpl, VTensorCacheEngine, VTensorMetadata, prepare_step
+    h, kvh, layers = 8, 2, 2
+    eng = VTensorCacheEngine(layers, kvh, 128, 3, 1024)
+    impl = VTensorAttentionImpl(h, 128, SCALE, kvh)
+    rs = np.random.RandomState(78)
+    slots = [1, 2]
+    ctx = [0, 0]
+    hist_k = [[torch.empty(0, kvh, 128, dtype=torch.bfloat16) for _ in slots] for _ in range(layers)]
+    hist_v = [[torch.empty(0, kvh, 128, dtype=torch.bfloat16) for _ in slots] for _ in range(layers)]
+    try:
+        for phase, new in enumerate([[300, 77], [50, 200], [1, 1], [1, 1]]):
+            decode = phase >= 2
+            ctx = [a + b for a, b in zip(ctx, new)]
+            if decode:
+                meta = VTensorMetadata(slots, ctx, kvh, 128, num_decode_tokens=2)
+            else:
+                meta = VTensorMetadata(slots, ctx, kvh, 128, num_prefills=2, query_lens=new)
+            prepare_step(meta, eng)
+            n = sum(new)
+            starts = [0, new[0]]
+            for layer in range(layers):
+                q = synth.normal_bf16(rs, n, h * 128)
+                kk = synth.normal_bf16(rs, n, kvh * 128)
+                vv = synth.normal_bf16(rs, n, kvh * 128)
+                kc, vc = eng.gpu_cache[layer]
+                maps = eng.prefill_maps(layer) if use_maps else None
+                out = impl.forward(q.cuda(), kk.cuda(), vv.cuda(), kc, vc, meta, prefill_maps=maps).cpu()
+                for i in range(2):
+                    rows = slice(starts[i], starts[i] + new[i])
+                    hist_k[layer][i] = torch.cat([hist_k[layer][i], kk[rows].view(-1, kvh, 128)])
+                    hist_v[layer][i] = torch.cat([hist_v[layer][i], vv[rows].view(-1, kvh, 128)])
+                r = oracle.fill_ranges(hist_k[layer], hist_v[layer])
+                port = oracle.port_prefill_attn(q.view(n, h, 128), r, torch.arange(2), torch.tensor(ctx, dtype=torch.int32),
+                                                torch.tensor(new, dtype=torch.int32), torch.tensor(starts, dtype=torch.int32),
+                                                kvh, SCALE)
+                ok, err = close_2e3(out.view(n, h, 128), port, ulp_slack=True)
+                assert ok, (phase, layer, err)
+    finally:
+        eng.close()
+
+
 @pytest.mark.parametrize("h,kvh", [(8, 1), (8, 8)])
 def test_decode_runner_graph_replay_with_layer_overlap(G, oracle, h, kvh):
     """DecodeRunner: all layers of a step in one CUDA graph, consecutive layers
