@@ -104,6 +104,7 @@ __global__ void __launch_bounds__(kUThreads, 2) prefill_umma_kernel(PrefillParam
   const int pos0 = seq_len - q_len + j0;                    // position of the tile's first query row
   const int kv_end = min(seq_len, pos0 + kUM);              // keys any row of the tile may see
   const int n_tiles = (kv_end + kUN - 1) / kUN;
+  if (kv_end <= 0) return;                                  // q_lens > seq_lens: invalid entry, nothing to attend
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
   // Set-up, overlapped: the producer lane initialises the barriers and at once starts the first K/V
