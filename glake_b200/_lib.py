@@ -86,7 +86,7 @@ def _load():
         "vt_ar_ipc_close": (c_int, [vp]),
         "vt_ar_create": (c_int, [c_int, c_int, POINTER(vp), sz, c_int, POINTER(vp)]),
         "vt_ar_destroy": (c_int, [vp]),
-        "vt_ar_configure": (c_int, [vp, ctypes.c_longlong, ctypes.c_longlong]),
+        "vt_ar_configure": (c_int, [vp, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong]),
         "vt_ar_status": (c_int, [vp, POINTER(ctypes.c_uint32)]),
         "vt_all_reduce": (c_int, [vp, vp, vp, sz, vp]),
         "vt_all_reduce_emulated": (c_int, [POINTER(vp), POINTER(vp), POINTER(vp), c_int, sz, vp]),

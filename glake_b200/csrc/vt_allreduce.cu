@@ -24,6 +24,15 @@
 // CTA b reuses staging[parity] two calls later, after it passed barrier A of the
 // call in between, which every peer's CTA b signals only after it finished reading.
 //
+// Messages up to 64 KiB skip the flags altogether ("push" path): every rank stores its
+// vectors straight into a per-source slot of every peer's receive buffer and then
+// polls its own slots until no 32-bit word holds the sentinel 0x80008000 any more (the
+// data is its own flag; an input word equal to the sentinel, two negative zeros, is
+// sent as +0, +0).  Three receive buffers rotate: call n uses buffer n % 3 and restores
+// the sentinel in the range call n - 1 used, which is safe because a peer can write
+// into that buffer again only after it has seen this rank's data of call n + 1.  That
+// leaves one NVLink one-way latency plus a local poll on the critical path.
+//
 // Every wait is bounded by wall time (%globaltimer); when it runs out the CTA sets
 // the status word, keeps signalling so that nobody else waits for it, and returns.
 // Peer data moves with plain loads and stores only (no multimem, no TMA).
@@ -43,13 +52,17 @@ constexpr int kArMaxCtas = 64;
 constexpr int kArThreads = 512;
 constexpr size_t kArFlagBytes = 4096;                        // one flag array: [64 CTAs][8 ranks] u32 = 2 KiB, padded
 constexpr uint32_t kArTimedOut = 0xDEAD0A88u;
+constexpr size_t kPushBytes = 64u << 10;                     // largest message of the push path
+constexpr uint32_t kSentinel = 0x80008000u;                  // (-0.0, -0.0) in bf16: "not written yet"
 
 struct ArDev {                                               // lives in local device memory
-  int rank, world, n_ctas, one_shot_vecs;
+  int rank, world, n_ctas, one_shot_vecs, push_vecs;
   unsigned long long wait_ns;
   size_t max_bytes;
   char *peer[kArMaxWorld];                                   // shared buffer of every rank, as mapped here
   uint32_t *epoch;                                           // [n_ctas] call numbers (local)
+  uint32_t *push_epoch;                                      // [n_ctas] number of push-path calls (local)
+  uint32_t *push_prev;                                       // [n_ctas] vectors of the previous push-path call (local)
   uint32_t *status;                                          // local
 };
 
@@ -66,6 +79,11 @@ __device__ __forceinline__ uint4 *staging(char *buf, size_t max_bytes, int parit
 }
 __device__ __forceinline__ uint4 *result(char *buf, size_t max_bytes, int parity) {
   return reinterpret_cast<uint4 *>(buf + 2 * kArFlagBytes + (2 + parity) * max_bytes);
+}
+
+// push path: receive buffer t (0..2), slot of source rank r
+__device__ __forceinline__ uint4 *push_slot(char *buf, size_t max_bytes, int t, int r) {
+  return reinterpret_cast<uint4 *>(buf + 2 * kArFlagBytes + 4 * max_bytes + (static_cast<size_t>(t) * kArMaxWorld + r) * kPushBytes);
 }
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
@@ -187,22 +205,90 @@ __device__ __forceinline__ void all_reduce_body(const ArDev &d, const uint4 *in,
   }
 }
 
+template <int W>
+__device__ __forceinline__ void push_body(const ArDev &d, const uint4 *in, uint4 *out, int n_vec, int *timed_out) {
+  const int b = blockIdx.x;
+  const uint32_t e = d.push_epoch[b] + 1;
+  const int n_prev = static_cast<int>(d.push_prev[b]);
+  const int cur = e % 3, clr = (e + 2) % 3;                  // clr held the data of push call e - 1
+  const int per = (n_vec + d.n_ctas - 1) / d.n_ctas;
+  const int lo = min(b * per, n_vec), hi = min(lo + per, n_vec);
+  char *me = d.peer[d.rank];
+  // 1. this rank's vectors into its slot of every rank's buffer
+  for (int v = lo + threadIdx.x; v < hi; v += kArThreads) {
+    uint4 x = in[v];
+    x.x = x.x == kSentinel ? 0u : x.x; x.y = x.y == kSentinel ? 0u : x.y;
+    x.z = x.z == kSentinel ? 0u : x.z; x.w = x.w == kSentinel ? 0u : x.w;
+#pragma unroll
+    for (int r = 0; r < W; ++r) push_slot(d.peer[r], d.max_bytes, cur, d.rank)[v] = x;
+  }
+  // 2. restore the sentinel where the previous push call landed (this CTA's slice of that extent)
+  {
+    const int per_p = (n_prev + d.n_ctas - 1) / d.n_ctas;
+    const int lo_p = min(b * per_p, n_prev), hi_p = min(lo_p + per_p, n_prev);
+    const uint4 s4 = make_uint4(kSentinel, kSentinel, kSentinel, kSentinel);
+    for (int v = lo_p + threadIdx.x; v < hi_p; v += kArThreads)
+#pragma unroll
+      for (int r = 0; r < W; ++r) push_slot(me, d.max_bytes, clr, r)[v] = s4;
+  }
+  // 3. wait for every rank's vector (the data is the flag), sum in rank order
+  bool ok = true;
+  for (int v = lo + threadIdx.x; v < hi; v += kArThreads) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < W; ++r) {
+      const uint4 *src = push_slot(me, d.max_bytes, cur, r) + v;
+      uint4 x = ld_relaxed_sys(src);
+      if (x.x == kSentinel || x.y == kSentinel || x.z == kSentinel || x.w == kSentinel) {
+        const unsigned long long t0 = global_ns();
+        for (unsigned it = 0;; ++it) {
+          x = ld_relaxed_sys(src);
+          if (x.x != kSentinel && x.y != kSentinel && x.z != kSentinel && x.w != kSentinel) break;
+          if ((it & 63u) == 63u && global_ns() - t0 > d.wait_ns) {
+            ok = false;
+            break;
+          }
+        }
+      }
+      add8(acc, x);
+    }
+    if (ok) out[v] = make_uint4(pack2(acc[0], acc[1]), pack2(acc[2], acc[3]), pack2(acc[4], acc[5]), pack2(acc[6], acc[7]));
+  }
+  if (!ok) *timed_out = 1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    d.push_epoch[b] = e;
+    d.push_prev[b] = static_cast<uint32_t>(n_vec);
+    if (*timed_out) atomicExch(d.status, kArTimedOut);
+  }
+}
+
+__global__ void __launch_bounds__(kArThreads) fill_words_kernel(uint32_t *p, size_t n, uint32_t value) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(kArThreads) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * kArThreads)
+    p[i] = value;
+}
+
 __global__ void __launch_bounds__(kArThreads, 2) all_reduce_kernel(const __grid_constant__ ArLaunch L, int n_vec) {
   __shared__ int timed_out;
   const ArDev &d = L.dev[blockIdx.y];
   const uint4 *in = static_cast<const uint4 *>(L.in[blockIdx.y]);
   uint4 *out = static_cast<uint4 *>(L.out[blockIdx.y]);
   if (threadIdx.x == 0) timed_out = 0;
+  __syncthreads();
+  const bool push = n_vec <= d.push_vecs;
+#define VT_AR_CASE(W)                                              \
+  case W:                                                          \
+    if (push) push_body<W>(d, in, out, n_vec, &timed_out);         \
+    else all_reduce_body<W>(d, in, out, n_vec, &timed_out);        \
+    break;
   switch (d.world) {
-    case 1: all_reduce_body<1>(d, in, out, n_vec, &timed_out); break;
-    case 2: all_reduce_body<2>(d, in, out, n_vec, &timed_out); break;
-    case 3: all_reduce_body<3>(d, in, out, n_vec, &timed_out); break;
-    case 4: all_reduce_body<4>(d, in, out, n_vec, &timed_out); break;
-    case 5: all_reduce_body<5>(d, in, out, n_vec, &timed_out); break;
-    case 6: all_reduce_body<6>(d, in, out, n_vec, &timed_out); break;
-    case 7: all_reduce_body<7>(d, in, out, n_vec, &timed_out); break;
-    default: all_reduce_body<8>(d, in, out, n_vec, &timed_out); break;
+    VT_AR_CASE(1) VT_AR_CASE(2) VT_AR_CASE(3) VT_AR_CASE(4) VT_AR_CASE(5) VT_AR_CASE(6) VT_AR_CASE(7)
+    default:
+      if (push) push_body<8>(d, in, out, n_vec, &timed_out);
+      else all_reduce_body<8>(d, in, out, n_vec, &timed_out);
+      break;
   }
+#undef VT_AR_CASE
 }
 
 }  // namespace
@@ -215,7 +301,8 @@ struct vt_ar {
 };
 
 namespace {
-size_t shared_bytes(size_t max_bytes) { return 2 * vt::kArFlagBytes + 4 * max_bytes; }
+size_t push_bytes_total() { return 3 * vt::kArMaxWorld * vt::kPushBytes; }
+size_t shared_bytes(size_t max_bytes) { return 2 * vt::kArFlagBytes + 4 * max_bytes + push_bytes_total(); }
 bool cuda_ok(cudaError_t e) { return e == cudaSuccess; }
 }  // namespace
 
@@ -269,8 +356,8 @@ int vt_ar_create(int rank, int world, void *const *peer_bufs, size_t max_bytes, 
   vt_ar *ar = new (std::nothrow) vt_ar();
   if (!ar) return VT_ERR_CUDA;
   if (!cuda_ok(cudaGetDevice(&ar->device)) ||
-      !cuda_ok(cudaMalloc(&ar->local, (vt::kArMaxCtas + 1) * sizeof(uint32_t))) ||
-      !cuda_ok(cudaMemset(ar->local, 0, (vt::kArMaxCtas + 1) * sizeof(uint32_t)))) {
+      !cuda_ok(cudaMalloc(&ar->local, (3 * vt::kArMaxCtas + 1) * sizeof(uint32_t))) ||
+      !cuda_ok(cudaMemset(ar->local, 0, (3 * vt::kArMaxCtas + 1) * sizeof(uint32_t)))) {
     cudaFree(ar->local);
     delete ar;
     return VT_ERR_CUDA;
@@ -283,8 +370,19 @@ int vt_ar_create(int rank, int world, void *const *peer_bufs, size_t max_bytes, 
   h.wait_ns = 1000000000ull;                                  // 1 s
   h.max_bytes = max_bytes;
   for (int r = 0; r < vt::kArMaxWorld; ++r) h.peer[r] = r < world ? static_cast<char *>(peer_bufs[r]) : nullptr;
+  h.push_vecs = static_cast<int>(vt::kPushBytes / 16);
   h.epoch = ar->local;
-  h.status = ar->local + vt::kArMaxCtas;
+  h.push_epoch = ar->local + vt::kArMaxCtas;
+  h.push_prev = ar->local + 2 * vt::kArMaxCtas;
+  h.status = ar->local + 3 * vt::kArMaxCtas;
+  // the receive buffers of the push path start out as "nothing written" (own buffer only: every rank does its own)
+  char *push0 = static_cast<char *>(peer_bufs[rank]) + 2 * vt::kArFlagBytes + 4 * max_bytes;
+  vt::fill_words_kernel<<<64, vt::kArThreads>>>(reinterpret_cast<uint32_t *>(push0), push_bytes_total() / 4, vt::kSentinel);
+  if (!cuda_ok(cudaGetLastError()) || !cuda_ok(cudaDeviceSynchronize())) {
+    cudaFree(ar->local);
+    delete ar;
+    return VT_ERR_CUDA;
+  }
   *out = ar;
   return VT_OK;
 }
@@ -296,8 +394,10 @@ int vt_ar_destroy(vt_ar *ar) {
   return VT_OK;
 }
 
-int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes) {
+int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes, long long push_bytes) {
   if (!ar) return VT_ERR_INVALID;
+  if (push_bytes >= 0)
+    ar->host.push_vecs = static_cast<int>(std::min<long long>(push_bytes, static_cast<long long>(vt::kPushBytes)) / 16);
   if (wait_ns > 0) ar->host.wait_ns = static_cast<unsigned long long>(wait_ns);
   if (one_shot_bytes >= 0)
     ar->host.one_shot_vecs = static_cast<int>(std::min<long long>(one_shot_bytes / 16, 1 << 30));

@@ -128,6 +128,8 @@ def allreduce_main():
     comm = tp.PeerAllReduce(max_size=max(max(sizes), 1 << 20))
     if os.environ.get("VT_AR_ONE_SHOT_BYTES"):
         comm.configure(one_shot_bytes=int(os.environ["VT_AR_ONE_SHOT_BYTES"]))
+    if os.environ.get("VT_AR_PUSH_BYTES"):
+        comm.configure(push_bytes=int(os.environ["VT_AR_PUSH_BYTES"]))
     calls = 100
     for nbytes in sizes:
         x = torch.randn(nbytes // 2, device='cuda').bfloat16(); y = torch.empty_like(x)

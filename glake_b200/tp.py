@@ -142,9 +142,9 @@ class PeerAllReduce:
             self._check(self._lib.vt_ar_status(self._ar, ctypes.byref(st)), "vt_ar_status")
         return st.value
 
-    def configure(self, wait_ns=0, one_shot_bytes=-1):
+    def configure(self, wait_ns=0, one_shot_bytes=-1, push_bytes=-1):
         with torch.cuda.device(self.device):
-            self._check(self._lib.vt_ar_configure(self._ar, wait_ns, one_shot_bytes), "vt_ar_configure")
+            self._check(self._lib.vt_ar_configure(self._ar, wait_ns, one_shot_bytes, push_bytes), "vt_ar_configure")
 
     def close(self):
         if self._ar:

@@ -373,10 +373,14 @@ int vt_fused_add_rms_norm(void *input, void *residual, const void *weight, float
  *   vt_ar_status         0, or non-zero once a wait for a peer ran out of time
  *                        (default 1 s; the results of that call are invalid and the
  *                        communicator should be dropped); synchronises.
- *   vt_ar_configure      wait limit in ns (<= 0 keeps it) and the message size up
+ *   vt_ar_configure      wait limit in ns (<= 0 keeps it); the message size up
  *                        to which every rank reads everything itself (one-shot)
  *                        instead of reduce-scatter + all-gather (< 0 keeps it;
- *                        default 6 MiB / (world - 1); two ranks are always one-shot).
+ *                        default 6 MiB / (world - 1); two ranks are always one-shot);
+ *                        the message size up to which the flag-free push path is
+ *                        used (< 0 keeps it, 0 disables it; default and maximum
+ *                        64 KiB).  On the push path an input word holding two
+ *                        negative zeros is summed as two positive zeros.
  *   vt_all_reduce_emulated   runs all `world` ranks of one call as ONE cooperative
  *                        launch on a single GPU (every vt_ar created on that GPU
  *                        with the same peer_bufs): the way to exercise the protocol
@@ -391,7 +395,7 @@ int vt_ar_ipc_open(const unsigned char handle[64], void **buf);
 int vt_ar_ipc_close(void *buf);
 int vt_ar_create(int rank, int world, void *const *peer_bufs, size_t max_bytes, int n_ctas, vt_ar **out);
 int vt_ar_destroy(vt_ar *ar);
-int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes);
+int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes, long long push_bytes);
 int vt_ar_status(vt_ar *ar, uint32_t *status);
 int vt_all_reduce(vt_ar *ar, const void *in, void *out, size_t n_elems, void *stream);
 int vt_all_reduce_emulated(vt_ar *const *ars, const void *const *ins, void *const *outs, int world,

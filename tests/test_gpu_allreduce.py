@@ -67,7 +67,7 @@ def test_emulated_ranks_match_the_oracle(oracle, world):
     E = Emulated(world)
     try:
         for a in E.ars:                                    # two-shot above 128 KiB, whatever the world size
-            E.check(E.lib.vt_ar_configure(a, 0, 128 << 10), "vt_ar_configure")
+            E.check(E.lib.vt_ar_configure(a, 0, 128 << 10, -1), "vt_ar_configure")
         # one-shot sizes, two-shot sizes, ragged vector counts, consecutive calls on both parities
         for call, n in enumerate([8, 8 * 37, 4096, 65536, 65536 + 8 * 5, 1 << 19, (1 << 19) + 8 * 123, 1 << 20, 8 * 3,
                                   1 << 20, 1 << 20]):
@@ -84,6 +84,44 @@ def test_emulated_ranks_match_the_oracle(oracle, world):
         E.close()
 
 
+@pytest.mark.parametrize("world", [2, 5, 8])
+def test_emulated_push_path_buffer_rotation(oracle, world):
+    """Messages up to 64 KiB take the flag-free path: data pushed into per-source slots,
+    the sentinel restored one call later, three buffers in rotation.  Sizes shrink and grow
+    from call to call (the restored range is the previous call's, not this one's), calls of
+    the flag path sit in between, and an input word of two negative zeros — the sentinel's
+    bit pattern — must come out as a zero sum."""
+    E = Emulated(world)
+    try:
+        sizes = [8, 32768, 8, 8 * 511, 32768, 32768, 1 << 18, 8 * 3, 32768, 8, 8, 8, 1 << 17, 4096, 32768]
+        for call, n in enumerate(sizes):
+            ins = _inputs(5000 + 10 * world + call, world, n)
+            if n >= 16:
+                for t in ins:
+                    t[8:10] = -0.0                                    # every rank sends the sentinel pattern there
+                    t[12] = -0.0                                      # half a word of it: an ordinary value
+            want = oracle.port_all_reduce(ins)
+            d_in = [t.cuda() for t in ins]
+            d_out = [torch.empty_like(t) for t in d_in] if call % 3 else d_in
+            assert E.run(d_in, d_out) == 0
+            torch.cuda.synchronize()
+            for r in range(world):
+                got = d_out[r].cpu()
+                assert torch.equal(got.float(), want.float()), f"call {call} n {n} rank {r}"   # == treats -0 and +0 alike
+        assert all(E.status(r) == 0 for r in range(world))
+        # the same messages with the push path switched off give the same values
+        for a in E.ars:
+            E.check(E.lib.vt_ar_configure(a, 0, -1, 0), "vt_ar_configure")
+        ins = _inputs(77, world, 4096)
+        d_in = [t.cuda() for t in ins]
+        outs = [torch.empty_like(t) for t in d_in]
+        assert E.run(d_in, outs) == 0
+        torch.cuda.synchronize()
+        assert all(torch.equal(o.cpu(), oracle.port_all_reduce(ins)) for o in outs)
+    finally:
+        E.close()
+
+
 def test_emulated_forced_modes_agree(oracle):
     """The same message through the one-shot and the two-shot path gives the same bits."""
     E = Emulated(4)
@@ -93,7 +131,7 @@ def test_emulated_forced_modes_agree(oracle):
         d_in = [t.cuda() for t in ins]
         for one_shot_bytes in (1 << 30, 0):
             for a in E.ars:
-                E.check(E.lib.vt_ar_configure(a, 0, one_shot_bytes), "vt_ar_configure")
+                E.check(E.lib.vt_ar_configure(a, 0, one_shot_bytes, -1), "vt_ar_configure")
             outs = [torch.empty_like(t) for t in d_in]
             assert E.run(d_in, outs) == 0
             torch.cuda.synchronize()
@@ -109,7 +147,7 @@ def test_a_missing_peer_ends_in_a_status_not_a_hang():
     from glake_b200._lib import VT_ERR_TOO_LARGE, VT_ERR_UNSUPPORTED
     E = Emulated(2, max_bytes=1 << 16)
     try:
-        E.check(E.lib.vt_ar_configure(E.ars[0], 2_000_000, -1), "vt_ar_configure")       # 2 ms
+        E.check(E.lib.vt_ar_configure(E.ars[0], 2_000_000, -1, -1), "vt_ar_configure")       # 2 ms
         x = torch.ones(1024, dtype=torch.bfloat16, device="cuda")
         y = torch.empty_like(x)
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
