@@ -24,7 +24,7 @@
 // CTA b reuses staging[parity] two calls later, after it passed barrier A of the
 // call in between, which every peer's CTA b signals only after it finished reading.
 //
-// Messages up to 64 KiB skip the flags altogether ("push" path): every rank stores its
+// Messages up to 256 KiB skip the flags altogether ("push" path): every rank stores its
 // vectors straight into a per-source slot of every peer's receive buffer and then
 // polls its own slots until no 32-bit word holds the sentinel 0x80008000 any more (the
 // data is its own flag; an input word equal to the sentinel, two negative zeros, is
@@ -52,7 +52,7 @@ constexpr int kArMaxCtas = 64;
 constexpr int kArThreads = 512;
 constexpr size_t kArFlagBytes = 4096;                        // one flag array: [64 CTAs][8 ranks] u32 = 2 KiB, padded
 constexpr uint32_t kArTimedOut = 0xDEAD0A88u;
-constexpr size_t kPushBytes = 64u << 10;                     // largest message of the push path
+constexpr size_t kPushBytes = 256u << 10;                    // largest message of the push path
 constexpr uint32_t kSentinel = 0x80008000u;                  // (-0.0, -0.0) in bf16: "not written yet"
 
 struct ArDev {                                               // lives in local device memory

@@ -379,7 +379,7 @@ int vt_fused_add_rms_norm(void *input, void *residual, const void *weight, float
  *                        default 6 MiB / (world - 1); two ranks are always one-shot);
  *                        the message size up to which the flag-free push path is
  *                        used (< 0 keeps it, 0 disables it; default and maximum
- *                        64 KiB).  On the push path an input word holding two
+ *                        256 KiB).  On the push path an input word holding two
  *                        negative zeros is summed as two positive zeros.
  *   vt_all_reduce_emulated   runs all `world` ranks of one call as ONE cooperative
  *                        launch on a single GPU (every vt_ar created on that GPU

@@ -86,14 +86,14 @@ def test_emulated_ranks_match_the_oracle(oracle, world):
 
 @pytest.mark.parametrize("world", [2, 5, 8])
 def test_emulated_push_path_buffer_rotation(oracle, world):
-    """Messages up to 64 KiB take the flag-free path: data pushed into per-source slots,
+    """Messages up to 256 KiB take the flag-free path: data pushed into per-source slots,
     the sentinel restored one call later, three buffers in rotation.  Sizes shrink and grow
     from call to call (the restored range is the previous call's, not this one's), calls of
     the flag path sit in between, and an input word of two negative zeros — the sentinel's
     bit pattern — must come out as a zero sum."""
     E = Emulated(world)
     try:
-        sizes = [8, 32768, 8, 8 * 511, 32768, 32768, 1 << 18, 8 * 3, 32768, 8, 8, 8, 1 << 17, 4096, 32768]
+        sizes = [8, 32768, 8, 8 * 511, 1 << 17, 32768, 1 << 18, 8 * 3, 1 << 17, 8, 8, 8, 1 << 19, 4096, 32768]
         for call, n in enumerate(sizes):
             ins = _inputs(5000 + 10 * world + call, world, n)
             if n >= 16:
