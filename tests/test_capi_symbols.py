@@ -46,3 +46,27 @@ def test_argument_validation_needs_no_gpu():
     assert L.vt_pool_create(0, 1, 12345, ctypes.byref(ctypes.c_void_p())) in (_lib.VT_ERR_INVALID,
                                                                                _lib.VT_ERR_NO_DRIVER,
                                                                                _lib.VT_ERR_DRIVER)
+
+
+def test_header_is_plain_c_and_links_against_the_library(tmp_path):
+    """include/vtensor.h must be consumable from C (the reference's FFI side may be C, cgo, JNI ...):
+    a C99 translation unit including it compiles without warnings and links against libvtensor.so."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        import pytest
+        pytest.skip("no C compiler")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "use_header.c"
+    src.write_text('#include "vtensor.h"\n#include <stdio.h>\n'
+                   'int main(void) { size_t b = 0; if (vt_ar_buffer_bytes(1u << 20, &b) != VT_OK) return 2;\n'
+                   '  printf("%s %zu %s\\n", vt_version(), b, vt_strerror(VT_ERR_TOO_LARGE)); return 0; }\n')
+    exe = tmp_path / "use_header"
+    lib_dir = os.path.join(root, "glake_b200")
+    res = subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-I", os.path.join(root, "include"),
+                          str(src), "-o", str(exe), "-L", lib_dir, "-l:libvtensor.so", f"-Wl,-rpath,{lib_dir}"],
+                         capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    run = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert run.returncode == 0 and "sm_100a" in run.stdout, run.stdout + run.stderr
