@@ -15,6 +15,12 @@ rotary_embedding (GLakeServe/csrc/cpu/pos_encoding.cpp:169-198) and rms_norm /
 fused_add_rms_norm (GLakeServe/csrc/cpu/layernorm.cpp:90-117); the rotated q / k
 and the normalised rows are stored as bf16 bit patterns.
 
+tests/synth.py:PREFILL_CASES: the reference's CPU backend has no prefix-prefill kernel
+(its prompt path is xformers), so every new token is run through the reference's
+CPU paged_attention_v1 as a decode query of its own over the tokens it may see
+(context = its position + 1), which is what causal attention over prefix + new
+tokens means; the outputs are stored in query order.
+
 Usage: python tests/golden/make_golden.py
 """
 import os
@@ -93,6 +99,29 @@ def run_norm_case(name):
     print(name, tuple(x.shape))
 
 
+def run_prefill_case(name):
+    seed, lens, q_lens, h, kvh = synth.PREFILL_CASES[name]
+    _, k, v = synth.make_case(seed, lens, h, kvh)
+    q = synth.make_prefill_queries(seed, q_lens, h)
+    ref = O.load_ref("bf16")
+    cache = O.RefPagedCache(ref, k, v)
+    rows, tables, ctx = [], [], []
+    start = 0
+    for i, (n, m) in enumerate(zip(lens, q_lens)):
+        for j in range(m):
+            rows.append(q[start + j])
+            tables.append(cache.block_tables[i])
+            ctx.append(n - m + j + 1)
+        start += m
+    qq = torch.stack(rows).contiguous()
+    out = torch.empty_like(qq)
+    ref.paged_attention_v1(out, qq, cache.key_cache, cache.value_cache, kvh, float(128 ** -0.5), torch.stack(tables).contiguous(),
+                           torch.tensor(ctx, dtype=torch.int32), O.REF_BLOCK, max(ctx), None, "auto", 1.0)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), out_bits=bits(out),
+                        input_sha256=np.asarray(synth.digest(q, k, v)))
+    print(name, "queries", tuple(qq.shape), "max|out|", float(out.float().abs().max()))
+
+
 if __name__ == "__main__":
     for name in synth.GOLDEN_CASES:
         run_case(name)
@@ -100,3 +129,5 @@ if __name__ == "__main__":
         run_rope_case(name)
     for name in synth.NORM_CASES:
         run_norm_case(name)
+    for name in synth.PREFILL_CASES:
+        run_prefill_case(name)

@@ -80,3 +80,15 @@ def make_norm_case(seed, tokens, hidden):
     x, r = normal_bf16(rs, tokens, hidden), normal_bf16(rs, tokens, hidden)
     w = torch.from_numpy((1.0 + 0.1 * rs.standard_normal(hidden)).astype(np.float32)).bfloat16()
     return x, r, w
+
+
+# name -> (seed, contexts, new tokens per sequence, H, KVH): causal attention of the new tokens over prefix + new
+PREFILL_CASES = {
+    "prefill_gqa4": (41, [37, 130, 64], [37, 50, 1], 8, 2),
+    "prefill_mha_tile_edges": (42, [128, 129, 200], [128, 65, 127], 4, 4),
+}
+
+
+def make_prefill_queries(seed, q_lens, h, d=128):
+    rs = np.random.RandomState(seed + 4242)
+    return normal_bf16(rs, int(sum(q_lens)), h, d)

@@ -446,6 +446,30 @@ def test_prefill_attention_over_the_range(G, oracle, h, kvh):
         kv.close()
 
 
+@pytest.mark.parametrize("name", list(synth.PREFILL_CASES))
+def test_prefill_against_reference_golden(G, name):
+    """Both prefill kernels against golden vectors made by the reference's CPU decode kernel
+    (one decode query per new token over the tokens it may see)."""
+    from glake_b200 import ops
+    from tests.test_oracle import GOLDEN, _from_bits, prefill_case_inputs
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    lens, q_lens, h, kvh, q, k, v, starts = prefill_case_inputs(name)
+    assert synth.digest(q, k, v) == str(z["input_sha256"]), "input generator drifted"
+    gold = _from_bits(z["out_bits"])
+    kv = G.GpuKV(k, v, kvh)
+    try:
+        ql = torch.tensor(q_lens, dtype=torch.int32).cuda()
+        for maps in (None, kv.engine.prefill_maps(0)):
+            out = torch.zeros_like(q, device="cuda")
+            ops.prefill_attention(out, q.cuda(), kv.k_table, kv.v_table, kvh, SCALE, kv.meta.slot_mapping,
+                                  kv.meta.seq_lens_tensor, ql, starts.cuda(), max(q_lens), maps=maps)
+            torch.cuda.synchronize()
+            ok, err = close_2e3(out.cpu(), gold, ulp_slack=True)
+            assert ok, (maps is not None, err)
+    finally:
+        kv.close()
+
+
 @pytest.mark.parametrize("h,kvh", [(8, 2), (4, 4)])
 def test_prefill_long_prompts_both_copy_paths(G, oracle, h, kvh):
     """Prompts beyond 1536 tokens take the 112-row tile shape; contexts end inside a

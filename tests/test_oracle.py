@@ -168,6 +168,29 @@ def _from_bits(a):
     return torch.from_numpy(a.copy()).view(torch.bfloat16)
 
 
+def prefill_case_inputs(name):
+    seed, lens, q_lens, h, kvh = synth.PREFILL_CASES[name]
+    _, k, v = synth.make_case(seed, lens, h, kvh)
+    q = synth.make_prefill_queries(seed, q_lens, h)
+    starts = np.concatenate([[0], np.cumsum(q_lens)[:-1]]).astype(np.int32)
+    return lens, q_lens, h, kvh, q, k, v, torch.from_numpy(starts)
+
+
+@pytest.mark.parametrize("name", list(synth.PREFILL_CASES))
+def test_port_prefill_matches_reference_golden(oracle, name):
+    """Causal prefix attention of the restatement against the reference's CPU decode kernel run
+    once per new token (stored golden): same fp32 algorithm, at most one bf16 rounding flip."""
+    z = np.load(os.path.join(GOLDEN, name + ".npz"))
+    lens, q_lens, h, kvh, q, k, v, starts = prefill_case_inputs(name)
+    assert synth.digest(q, k, v) == str(z["input_sha256"]), "input generator drifted"
+    gold = _from_bits(z["out_bits"])
+    r = oracle.fill_ranges(k, v)
+    out = oracle.port_prefill_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32),
+                                   torch.tensor(q_lens, dtype=torch.int32), starts, kvh, SCALE)
+    assert one_ulp_close(out, gold, 1e-5)
+    assert (out == gold).float().mean() > 0.99
+
+
 @pytest.mark.parametrize("name", list(synth.ROPE_CASES))
 def test_port_rotary_matches_golden(oracle, name):
     """The restated rotary embedding reproduces the reference CPU kernel's q and k bit for bit."""
