@@ -14,7 +14,7 @@ VT_OK = 0
 VT_ERR_INVALID, VT_ERR_DRIVER, VT_ERR_POOL_EMPTY, VT_ERR_RESERVE, VT_ERR_TIMEOUT = 1, 2, 3, 4, 5
 VT_ERR_UNSUPPORTED, VT_ERR_CUDA, VT_ERR_STATE, VT_ERR_NO_DRIVER, VT_ERR_KERNEL = 6, 7, 8, 9, 10
 VT_ERR_TOO_LARGE = 11
-VT_STATIC_SCRATCH_BYTES = 16 << 20
+VT_STATIC_SCRATCH_BYTES = 24 << 20
 VT_STEP_OVERLAP = 1
 VT_KV_BF16, VT_KV_FP8_E4M3 = 0, 1
 
@@ -106,6 +106,7 @@ def _load():
                                           c_float, c_int, vp, vp, vp, c_int, vp]),
         "vt_decode_attn_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int), POINTER(c_int),
                                         POINTER(c_int)]),
+        "vt_attn_set_tuning": (c_int, [c_int, c_int]),
         "vt_decode_attn_status": (c_int, [vp, vp, POINTER(c_int)]),
     }
     for name, (res, args) in sigs.items():

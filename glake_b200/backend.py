@@ -14,6 +14,7 @@
 PyTorch supplies device memory and the current stream; the work is done by the
 CUDA kernels behind :mod:`glake_b200.ops`.
 """
+import time
 from dataclasses import dataclass, field
 from typing import List, Optional
 
@@ -225,8 +226,14 @@ class DecodeRunner:
     BUCKET = 2048  # graphs are keyed by max context rounded up to this many tokens
 
     def __init__(self, engine: VTensorCacheEngine, impl: VTensorAttentionImpl, batch, host_io=False,
-                 k_scale=None, v_scale=None, overlap=True):
+                 k_scale=None, v_scale=None, overlap=True, post_layer=None, launches_per_post_layer=0):
+        """``post_layer(layer)``, when given, is called on the runner's stream after every
+        layer's attention, inside the captured graph: the place of what the model does
+        between two attention layers, e.g. the tensor-parallel all-reduces after o_proj
+        and down_proj (GLakeServe/vllm/model_executor/layers/linear.py:690-691)."""
         self.engine, self.impl, self.batch, self.host_io = engine, impl, batch, host_io
+        self.post_layer, self.launches_per_post_layer = post_layer, launches_per_post_layer
+        self.prepare_seconds = []     # host time of the allocator bookkeeping of each step
         # consecutive layers touch disjoint ranges: let layer l+1 start as layer l drains
         self.overlap = overlap and engine.num_layers > 1
         self.k_scale, self.v_scale = k_scale, v_scale
@@ -290,6 +297,8 @@ class DecodeRunner:
                             self.v[layer], kc.vmm_ptr, vc.vmm_ptr, self.d64[:b], self.d64[b:], self.d32[:b],
                             meta.max_seq_len, self.impl.num_kv_heads, self.impl.scale, self.impl.kv_cache_dtype,
                             ks, vs, overlap=self.overlap and layer > 0, workspace=self.workspace)
+            if self.post_layer is not None:
+                self.post_layer(layer)
             if self.host_io and ((layer + 1) % self.io_group == 0 or layer == n_layers - 1):
                 l0 = layer - layer % self.io_group
                 self.ev_out[layer].record(main)
@@ -306,7 +315,9 @@ class DecodeRunner:
         in ``self.out`` (or ``self.hout``).  Asynchronous: returns after the replay
         has been enqueued on ``self.stream``."""
         assert len(meta.slot_mapping_list) == self.batch
+        t0 = time.perf_counter()
         slot_m, starts = prepare_step_host(meta, self.engine)
+        self.prepare_seconds.append(time.perf_counter() - t0)
         b = self.batch
         cur = self.n_steps % 2
         self.n_steps += 1
@@ -336,17 +347,28 @@ class DecodeRunner:
                 self._body(capture_meta)        # warm-up outside capture (sets kernel attributes)
                 self.stream.synchronize()
                 graph = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(graph, stream=self.stream):
+                # thread-local capture mode: with collectives in the step, the process group's
+                # watchdog thread may query events while the capture is open
+                with torch.cuda.graph(graph, stream=self.stream, capture_error_mode="thread_local"):
                     self._body(capture_meta)
             self.graphs[bucket] = graph
             _, parts, variant = ops.attn_plan(b, self.impl.num_heads, self.impl.num_kv_heads, bucket,
                                               self.impl.kv_cache_dtype)
             # fused step: one kernel per layer; otherwise append + attention (+ merge)
-            per_layer = 1 if variant == 2 else 2 + (1 if parts > 1 else 0)
-            self.kernel_launches_per_step = self.engine.num_layers * per_layer
+            fused = variant == 2 and ops.step_is_fused(self.impl.kv_cache_dtype)
+            per_layer = 1 if fused else 2 + (1 if parts > 1 else 0)
+            self.kernel_launches_per_step = self.engine.num_layers * (per_layer + self.launches_per_post_layer)
             return  # the warm-up pass above already executed this step
         with torch.cuda.stream(self.stream):
             graph.replay()
 
     def synchronize(self):
         self.stream.synchronize()
+
+    def status(self):
+        """0 unless one of this runner's kernels gave up on a bounded wait (its results
+        are then invalid).  Synchronises the runner's stream."""
+        if self.workspace is None:
+            return 0
+        with torch.cuda.stream(self.stream):
+            return ops.workspace_status(self.workspace)

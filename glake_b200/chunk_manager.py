@@ -17,8 +17,9 @@ the allocator can be driven by a real scheduler instead of a synthetic loop:
 All counts are per layer, exactly as in the reference, whose worker divides the
 physical budget by the layer count (GLakeServe/vllm/worker/worker.py:170-175);
 the allocator multiplies by ``2 * layers`` ranges when it maps.
-``apply`` connects a decision to the allocator objects of
-:mod:`glake_b200.vmmAllocator` (``eagerExtend`` / ``release_seq`` / ``preempt_seq``).
+``apply_allocate`` / ``apply_extend`` / ``apply_free`` connect a decision to the
+allocator objects of :mod:`glake_b200.vmmAllocator` (``ensure_mapped`` /
+``eagerExtend`` / ``release_seq`` / ``preempt_seq``).
 """
 from dataclasses import dataclass
 from enum import Enum
@@ -168,6 +169,17 @@ class ChunkSpaceManager:
 
     def free_blocks(self) -> int:
         return self.num_free
+
+
+def apply_allocate(seq: SequenceChunks, segment) -> None:
+    """Admission: map the sequence's whole logical reservation — the prompt plus the
+    headroom of ``PREFILL_HEADROOM_TOKENS`` rows — synchronously (the reference's prefill
+    growth maps ``used + tokens + 100 tokens``, vmm_allocator.cpp:322-337).  From then on
+    the logical accounting runs that many rows ahead of the fill position, so
+    ``append_slots`` lists a slot for background growth about 100 decode steps before
+    the kernels reach the new chunk: the 2 x layers driver calls of a growth (tens of
+    milliseconds for a deep model) never sit on a step's critical path."""
+    segment.ensure_mapped(seq.reserve_size)
 
 
 def apply_extend(extend_seq_list: List[int], segments, token_bytes: int) -> None:

@@ -43,7 +43,11 @@ int grow_chunks(vt_seg *seg, size_t n) {
   const size_t cb = pool->chunk_bytes;
   const size_t ranges = 2 * static_cast<size_t>(seg->n_layers);
   size_t mapped;
-  { std::lock_guard<std::mutex> g(seg->mu); mapped = seg->mapped; }
+  {
+    std::lock_guard<std::mutex> g(seg->mu);
+    if (seg->poisoned) return VT_ERR_STATE;
+    mapped = seg->mapped;
+  }
   if (mapped + n * cb > seg->reserve) return VT_ERR_RESERVE;
 
   std::vector<CUmemGenericAllocationHandle> take;
@@ -272,7 +276,9 @@ static int release_locked(vt_seg *seg, size_t keep_bytes) {  // caller holds op_
   int st = VT_OK;
   std::vector<CUmemGenericAllocationHandle> back;
   for (size_t r = 0; r < seg->chunks.size(); ++r) {
-    CUresult e = pool->drv->mem_unmap(vt::range_base(seg, r) + keep, mapped - keep);
+    // a range that an earlier, partly failed release already cut back
+    if (seg->chunks[r].size() <= keep_chunks) continue;
+    CUresult e = pool->drv->mem_unmap(vt::range_base(seg, r) + keep, seg->chunks[r].size() * cb - keep);
     pool->unmap_calls++;
     if (e != CUDA_SUCCESS) { vt::set_last_driver_error(e); st = VT_ERR_DRIVER; break; }
     std::lock_guard<std::mutex> g(seg->mu);
@@ -285,9 +291,13 @@ static int release_locked(vt_seg *seg, size_t keep_bytes) {  // caller holds op_
     std::lock_guard<std::mutex> g(pool->mu);
     pool->free_list.insert(pool->free_list.end(), back.begin(), back.end());
   }
-  if (st == VT_OK) {
+  {
+    // On failure the ranges before the failing one are already cut back to `keep`
+    // while the others still reach `mapped`: the segment stays unusable for growth,
+    // bookkeeping and table fills until a later release or destroy gets through.
     std::lock_guard<std::mutex> g(seg->mu);
-    seg->mapped = keep;
+    seg->poisoned = st != VT_OK;
+    if (st == VT_OK) seg->mapped = keep;
   }
   return st;
 }
@@ -414,6 +424,7 @@ int vt_extend_batch(vt_seg *const *segs, int n, const int64_t *set_used_tokens,
     int pending;
     {
       std::lock_guard<std::mutex> g(s->mu);
+      if (s->poisoned) return VT_ERR_STATE;
       used = (set_used_tokens && set_used_tokens[i] > 0) ? static_cast<size_t>(set_used_tokens[i]) * kv_size : s->used;
       mapped = s->mapped;
       pending = s->pending;

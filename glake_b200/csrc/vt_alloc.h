@@ -45,6 +45,9 @@ struct vt_seg {
   int pending = 0;    // queued or running background growths
   int async_status = VT_OK;
   uint64_t epoch = 0;  // bumped by release: queued growths of older epochs are dropped
+  // A release whose cuMemUnmap failed part-way leaves the ranges mapped to different
+  // frontiers; until a later release / destroy completes, growth and row bookkeeping are refused.
+  bool poisoned = false;
   // chunks[r] = handles mapped into range r (r = 2 * layer + {0: K, 1: V}), in address order
   std::vector<std::vector<CUmemGenericAllocationHandle>> chunks;
 };

@@ -38,20 +38,10 @@
 #include "vt_device.cuh"
 #include "vt_kernels.h"
 #include "vt_mma.cuh"
+#include "vt_mma_f8.cuh"
 
 namespace vt {
 namespace {
-
-#ifdef VT_TRACE
-__device__ __forceinline__ unsigned long long gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define VT_TR(slot) do { if (p.trace && (threadIdx.x & 31) == 0) p.trace[(blockIdx.x * 5 + (threadIdx.x >> 5)) * 8 + (slot)] = gtime(); } while (0)
-#else
-#define VT_TR(slot) do {} while (0)
-#endif
 
 // Ring depth and residency per engine.  The bf16 engine with one 8-head block runs
 // 3 CTAs per SM on 2-stage rings (66 KB, <= 128 registers): with more, shorter-lived
@@ -150,7 +140,6 @@ attn_flat_kernel(AttnParams p) {
   const int g = p.h / p.kvh;
   const int slabs = p.kvh / HS;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  VT_TR(0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(full0 + 8 * s, 1);
@@ -186,7 +175,6 @@ attn_flat_kernel(AttnParams p) {
     if (lane == 0) prefix[0] = 0;
   }
   __syncthreads();
-  VT_TR(1);
   pdl_launch_dependents();   // the next launch may be scheduled as CTAs of this grid exit
   const long long total = prefix[p.batch];
   // Only min(grid, total) CTAs take part, so that every participating CTA owns at
@@ -226,7 +214,6 @@ attn_flat_kernel(AttnParams p) {
           if (lane == 0) atomicExch(p.status, kKernelErrMagic);
           return;
         }
-        if (it == 0) VT_TR(2);
         const int t0 = tile * TILE_TOK;
         const int nt = min(TILE_TOK, seq_len - t0);
         if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2u * nt * HS * kRowB);
@@ -246,7 +233,6 @@ attn_flat_kernel(AttnParams p) {
       }
       tau += pc.tile_end - pc.tile_begin;
     }
-    VT_TR(5);
     return;
   }
 
@@ -297,7 +283,6 @@ attn_flat_kernel(AttnParams p) {
       const int s = it % kStages;
       if (!failed && !mbar_wait(full0 + 8 * s, (it / kStages) & 1)) failed = true;
       if (failed) continue;
-      if (it == 0) VT_TR(2);
       const int tok0 = tile * TILE_TOK + rr;      // token of fragment row 0
       if (!kFp8 && append_off >= 0 && (seq_len - 1 - tok0) % R == 0 && seq_len - 1 >= tok0 &&
           seq_len - 1 < (tile + 1) * TILE_TOK) {
@@ -315,7 +300,6 @@ attn_flat_kernel(AttnParams p) {
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
     }
     st.finish_sums();
-    VT_TR(3);
 
     const bool whole = pc.tile_begin == 0 && pc.tile_end == pc.tiles_in_stream;
     if (R == 1 && whole) {
@@ -466,13 +450,16 @@ attn_flat_kernel(AttnParams p) {
           *reinterpret_cast<uint2 *>(out + pc.b * p.out_stride + hq * kHeadDim + lane * 4) = packed;
           if (p.lse && lane == 0) p.lse[pc.b * p.h + hq] = (M + log2f(L)) * 0.6931471805599453f;
         }
+        // With R > 1 a stream that lies wholly inside this CTA is published to slot 1 and
+        // merged right here; the next piece publishes to slot 1 again.  No warp may start
+        // that store while another still reads this piece's rows (a warp without merge
+        // items would otherwise run ahead through a short piece).
+        if (R > 1) named_bar_sync(1, kCWarps * 32);
       }
     }
     first_piece = false;
     tau += pc.tile_end - pc.tile_begin;
-    VT_TR(4);
   }
-  VT_TR(5);
   if (failed && lane == 0) atomicExch(p.status, kKernelErrMagic);
 }
 
@@ -480,7 +467,7 @@ template <template <int> class W, int NB, int HS, int R>
 int launch(const AttnParams &p_in, cudaStream_t stream) {
   constexpr int kThreads = (W<NB>::kWarps + 1) * 32;
   AttnParams p = p_in;
-  p.n_ctas = std::min(FlatCfg<W, NB>::kCtasPerSm * sm_count(), kFlatMaxCtas);
+  p.n_ctas = FlatCfg<W, NB>::kCtasPerSm * std::min(sm_count(), kFlatSms);
   const int smem = flat_smem_bytes(p.batch, FlatCfg<W, NB>::kStages);
   static SmemOptIn opt_in;
   if (!opt_in.ensure(attn_flat_kernel<W, NB, HS, R>, smem)) return VT_ERR_CUDA;
@@ -529,6 +516,14 @@ bool attn_flat_supports(int batch, int h, int kvh, int kv_dtype) {
 }
 
 int flat_consumer_warps(int kv_dtype) { return kv_dtype == VT_KV_FP8_E4M3 ? 8 : 4; }
+
+// Largest grid launch() uses for this problem: the scratch holds two piece slots per CTA.
+int flat_max_ctas(int h, int kvh, int kv_dtype) {
+  const bool nb1 = (h / kvh) <= 8;
+  const int per_sm = kv_dtype == VT_KV_FP8_E4M3 ? (nb1 ? FlatCfg<WarpAttnF8, 1>::kCtasPerSm : FlatCfg<WarpAttnF8, 2>::kCtasPerSm)
+                                                : (nb1 ? FlatCfg<WarpAttn, 1>::kCtasPerSm : FlatCfg<WarpAttn, 2>::kCtasPerSm);
+  return per_sm * kFlatSms;
+}
 
 int launch_attn_flat(const AttnParams &p, int kv_dtype, cudaStream_t stream) {
   if (!attn_flat_supports(p.batch, p.h, p.kvh, kv_dtype)) return VT_ERR_UNSUPPORTED;

@@ -1,6 +1,7 @@
 // Split-K planning, the partial-result merge kernel, and the C entry points of
 // the device-side path.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -40,6 +41,24 @@ __global__ void __launch_bounds__(kHeadDim) attn_reduce_kernel(AttnParams p) {
 
 }  // namespace
 
+namespace {
+// Process-wide tuning override: variant -1 = the planner's choice, part_tokens 0 = likewise.
+struct Tuning { int variant, part_tokens; };
+std::atomic<int> g_tune_variant{-1}, g_tune_part{0};
+std::once_flag g_tune_env;
+Tuning tuning() {
+  std::call_once(g_tune_env, [] {
+    if (const char *v = getenv("VT_ATTN_VARIANT")) {
+      if (!strcmp(v, "simt")) g_tune_variant.store(0);
+      if (!strcmp(v, "mma")) g_tune_variant.store(1);
+      if (!strcmp(v, "flat")) g_tune_variant.store(2);
+    }
+    if (const char *v = getenv("VT_ATTN_PART_TOKENS")) g_tune_part.store(atoi(v));
+  });
+  return Tuning{g_tune_variant.load(std::memory_order_relaxed), g_tune_part.load(std::memory_order_relaxed)};
+}
+}  // namespace
+
 size_t attn_workspace_bytes(int batch, int h, int max_parts) {
   const size_t rows = static_cast<size_t>(batch) * h * max_parts;
   size_t ml = (rows * 2 * sizeof(float) + 255) / 256 * 256;
@@ -52,8 +71,9 @@ static size_t flat_counter_bytes(int batch, int kvh) {
 static size_t flat_workspace_bytes(int batch, int h, int kvh, int kv_dtype, bool worst_case = false) {
   const int heads = (!worst_case && (h / kvh) <= 8) ? 8 : 16;
   const int warps = worst_case ? 8 : flat_consumer_warps(kv_dtype);
+  const int ctas = worst_case ? kFlatMaxCtas : flat_max_ctas(h, kvh, kv_dtype);
   return kStatusBytes + flat_counter_bytes(batch, kvh) +
-         static_cast<size_t>(kFlatMaxCtas) * 2 * warps * heads * kFlatPartRow * sizeof(float);
+         static_cast<size_t>(ctas) * 2 * warps * heads * kFlatPartRow * sizeof(float);
 }
 
 size_t attn_workspace_bound(int batch, int h, int max_seq_len) {
@@ -85,13 +105,12 @@ int plan_attn(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_
   (void)g;
   plan->variant = attn_mma_supports(h, kvh, kv_dtype) ? 1 : 0;
   if (num_splits == 0 && attn_flat_supports(batch, h, kvh, kv_dtype)) plan->variant = 2;
-  // Tuning overrides (read per call; meant for benchmarking, not for production):
-  //   VT_ATTN_VARIANT=simt|mma   VT_ATTN_PART_TOKENS=<multiple of 32>
-  if (const char *v = getenv("VT_ATTN_VARIANT")) {
-    if (!strcmp(v, "simt")) plan->variant = 0;
-    if (!strcmp(v, "mma") && attn_mma_supports(h, kvh, kv_dtype)) plan->variant = 1;
-    if (!strcmp(v, "flat") && attn_flat_supports(batch, h, kvh, kv_dtype)) plan->variant = 2;
-  }
+  // Tuning override (vt_attn_set_tuning, or the VT_ATTN_VARIANT / VT_ATTN_PART_TOKENS
+  // environment variables read once when the library first plans a call).
+  const Tuning tn = tuning();
+  if (tn.variant == 0) plan->variant = 0;
+  if (tn.variant == 1 && attn_mma_supports(h, kvh, kv_dtype)) plan->variant = 1;
+  if (tn.variant == 2 && attn_flat_supports(batch, h, kvh, kv_dtype)) plan->variant = 2;
   int part;
   if (num_splits > 0) {
     part = (max_seq_len + num_splits - 1) / num_splits;
@@ -106,10 +125,7 @@ int plan_attn(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_
     part = static_cast<int>((max_seq_len + want_parts - 1) / want_parts);
     part = std::max(kMinPartTokens, std::min(1024, (part + 31) / 32 * 32));
   }
-  if (const char *v = getenv("VT_ATTN_PART_TOKENS")) {
-    const int forced = atoi(v);
-    if (forced >= 32) part = forced / 32 * 32;
-  }
+  if (tn.part_tokens >= 32) part = tn.part_tokens / 32 * 32;
   plan->part_tokens = part;
   plan->max_parts = std::max(1, (max_seq_len + part - 1) / part);
   plan->ws_bytes = attn_workspace_bytes(batch, h, plan->max_parts);
@@ -204,10 +220,9 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
       p.new_key_stride = new_key_stride; p.new_value_stride = new_value_stride; p.byte_off = byte_off;
     }
     vt::carve_flat(workspace, batch, kvh, &p);
-#ifdef VT_TRACE
-    p.trace = getenv("VT_TRACE_PTR") ? reinterpret_cast<unsigned long long *>(strtoull(getenv("VT_TRACE_PTR"), nullptr, 0)) : nullptr;
-#endif
-    p.overlap = (flags & VT_STEP_OVERLAP) ? 1 : 0;
+    // Overlap only for the fused launch: a separate append kernel in front of this one
+    // writes the row this launch reads, and only ordinary stream order covers that.
+    p.overlap = (fused && (flags & VT_STEP_OVERLAP)) ? 1 : 0;
     // The ticket counters return to zero at the end of every launch.  They are
     // cleared here anyway so that a scratch buffer of unknown content works — except
     // in overlap mode, where a memset between the kernels would serialise them and
@@ -261,12 +276,28 @@ int vt_decode_attn_static(void *out, int64_t out_stride, const void *q, int64_t 
   if (d != vt::kHeadDim || h % kvh != 0) return VT_ERR_UNSUPPORTED;
   vt::AttnPlan plan;
   vt::plan_attn(batch, h, kvh, std::max(max_seq_len, 1), kv_dtype, num_splits, &plan);
+  if (plan.ws_bytes > VT_STATIC_SCRATCH_BYTES && num_splits == 0) {
+    // The default schedule's scratch does not fit the array: see whether a split-K
+    // schedule does (4, then 2, then 1 partitions per sequence) before refusing.
+    for (int splits = 4; splits >= 1 && plan.ws_bytes > VT_STATIC_SCRATCH_BYTES; splits /= 2) {
+      vt::plan_attn(batch, h, kvh, std::max(max_seq_len, 1), kv_dtype, splits, &plan);
+      num_splits = splits;
+    }
+  }
   if (plan.ws_bytes > VT_STATIC_SCRATCH_BYTES) return VT_ERR_TOO_LARGE;
   void *scratch = static_scratch_for_current_device();
   if (!scratch) return VT_ERR_CUDA;
   return vt_decode_attn(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, batch, h, kvh, d,
                         max_seq_len, scale, kv_dtype, k_scale, v_scale, lse, scratch, VT_STATIC_SCRATCH_BYTES,
                         num_splits, stream);
+}
+
+int vt_attn_set_tuning(int variant, int part_tokens) {
+  if (variant < -1 || variant > 2 || part_tokens < 0 || (part_tokens != 0 && part_tokens < 32)) return VT_ERR_INVALID;
+  vt::tuning();   // the environment is read first, so that it cannot overwrite this later
+  vt::g_tune_variant.store(variant);
+  vt::g_tune_part.store(part_tokens);
+  return VT_OK;
 }
 
 int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype, int num_splits,

@@ -64,14 +64,12 @@ struct AttnParams {
   int64_t new_key_stride, new_value_stride;   // elements per batch row
   const int64_t *byte_off;            // destination byte offset per entry (negative = nothing to append)
   int overlap;                        // launched as a programmatic dependent of the previous kernel on the stream
-#ifdef VT_TRACE
-  unsigned long long *trace;          // debug builds only: per-CTA timestamps
-#endif
 };
 
 constexpr int kFlatMaxBatch = 1024;   // prefix table of the flat schedule lives in shared memory
 constexpr int kFlatPartRow = 132;     // floats per published piece state row (16-byte aligned)
-constexpr int kFlatMaxCtas = 444;     // 3 per SM on the 148 SMs of a B200 (a larger part just gets fewer per SM)
+constexpr int kFlatSms = 148;         // SMs of a B200; a part with more just runs the same grid on fewer CTAs per SM
+constexpr int kFlatMaxCtas = 3 * kFlatSms;   // upper bound of any engine's grid (3 resident CTAs per SM)
 
 struct PrefillParams {
   void *out; int64_t out_stride;      // bf16 [tokens, h, 128]; stride of a token row in elements
@@ -110,6 +108,7 @@ bool attn_mma_supports(int h, int kvh, int kv_dtype);
 int launch_attn_flat(const AttnParams &p, int kv_dtype, cudaStream_t stream);
 bool attn_flat_supports(int batch, int h, int kvh, int kv_dtype);
 int flat_consumer_warps(int kv_dtype);
+int flat_max_ctas(int h, int kvh, int kv_dtype);
 int launch_attn_reduce(const AttnParams &p, int kv_dtype, cudaStream_t stream);
 
 }  // namespace vt

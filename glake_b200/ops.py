@@ -256,6 +256,12 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
               "vt_decode_step")
 
 
+def step_is_fused(kv_cache_dtype):
+    """Whether decode_step on the persistent schedule is ONE launch (the attention kernel
+    appends the new rows itself) for this cache type; otherwise an append kernel runs first."""
+    return _kv_dtype(kv_cache_dtype) == VT_KV_BF16
+
+
 def prefill_tma_supported(num_kv_heads):
     """Whether ``prefill_maps`` / the TMA prefill path take this kv-head count (a
     32-token box must never straddle a 2 MiB chunk)."""
@@ -306,6 +312,24 @@ def attn_plan(batch, num_heads, num_kv_heads, max_seq_len, kv_cache_dtype="auto"
     check(lib.vt_decode_attn_plan(batch, num_heads, num_kv_heads, max_seq_len, _kv_dtype(kv_cache_dtype),
                                   num_splits, byref(a), byref(b), byref(c)), "vt_decode_attn_plan")
     return a.value, b.value, c.value
+
+
+_VARIANTS = {None: -1, "auto": -1, "simt": 0, "mma": 1, "flat": 2}
+
+
+def set_attn_tuning(variant="auto", part_tokens=0):
+    """Process-wide planner override for benchmarks and tests: ``variant`` one of
+    auto / simt / mma / flat, ``part_tokens`` tokens per split-K partition (0 = auto)."""
+    check(lib.vt_attn_set_tuning(_VARIANTS[variant], int(part_tokens)), "vt_attn_set_tuning")
+
+
+def workspace_status(workspace):
+    """VT_OK (0) unless an attention kernel using this scratch buffer gave up on a
+    bounded wait.  Synchronises the current stream."""
+    code = ctypes.c_int()
+    with torch.cuda.device(workspace.device):
+        check(lib.vt_decode_attn_status(_ptr(workspace), _stream(), byref(code)), "vt_decode_attn_status")
+    return code.value
 
 
 def attn_status(device=None):

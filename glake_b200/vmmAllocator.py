@@ -137,6 +137,12 @@ class KVcacheSegment:
         st = lib.vt_seg_grow(self._h, self.actual_size + int(expand_num) * granularitySize)
         return st == 0
 
+    def ensure_mapped(self, nbytes):
+        """Synchronous growth until at least ``nbytes`` of every range are mapped (whole
+        chunks); no-op when they already are.  Used at admission to map a sequence's
+        logical reservation (prompt + headroom) in one go."""
+        check(lib.vt_seg_grow(self._h, int(nbytes)), "vt_seg_grow")
+
     def eagerExtend(self, token_size, seq_id):
         """Queue one chunk per range on the worker thread (vmm_allocator.cpp:307-320)."""
         _slot_registry[int(seq_id)] = (self, int(token_size))
@@ -170,6 +176,29 @@ class KVcacheSegment:
         """Unmap everything (vmm_allocator.cpp:348-381)."""
         _slot_registry.pop(int(seq_id), None)
         check(lib.vt_seg_release(self._h, 0), "vt_seg_release")
+
+    def write_string(self, data):
+        """Debug helper (vmm_allocator.cpp:423-433): copies the bytes of ``data`` to the
+        fill position of layer 0's K range and advances the fill.  The target must be mapped."""
+        raw = data.encode() if isinstance(data, str) else bytes(data)
+        used = self.get_used_slot()
+        if used + len(raw) > self.actual_size:
+            raise RuntimeError("write_string: beyond the mapped part of the range")
+        if raw:
+            buf = ctypes.create_string_buffer(raw, len(raw))
+            check(lib.vt_pool_write(_require_pool(), self.getKeyDevicePtr(0) + used, buf, len(raw)), "vt_pool_write")
+            self.set_used_size(used + len(raw))
+
+    def read_string(self):
+        """Debug helper (vmm_allocator.cpp:435-446): prints layer 0's K range up to the fill
+        position, as the reference does, and also returns it."""
+        used = self.get_used_slot()
+        buf = ctypes.create_string_buffer(max(used, 1))
+        if used:
+            check(lib.vt_pool_read(_require_pool(), buf, self.getKeyDevicePtr(0), used), "vt_pool_read")
+        text = buf.raw[:used].decode(errors="replace")
+        print(text)
+        return text
 
     def show_info(self, seq_id):
         return [int(seq_id), self.actual_size, self.get_used_slot(), int(self.ready()), 0]
@@ -238,6 +267,10 @@ def wait_ready(seq_ids, timeout_us=WAIT_US):
 
 
 def query_unmap(seq_ids):
+    """Per slot: True when no unmap of it is in flight (vmm_allocator.cpp:105-111 returns
+    ``!unmap_ptr[slot]``, a flag the reference initialises to 0 and never sets).  Here
+    ``release_seq`` / ``preempt_seq`` unmap synchronously before they return, so there is
+    never one in flight by the time a caller can ask."""
     return [True for _ in seq_ids]
 
 

@@ -224,6 +224,15 @@ int vt_decode_attn(void *out, int64_t out_stride, const void *q, int64_t q_strid
                    float *lse, void *workspace, size_t workspace_bytes, int num_splits,
                    void *stream);
 
+/* Process-wide override of the planner, for benchmarks and tests (no counterpart
+ * in the reference).  variant: -1 = the planner's choice, 0 = SIMT split-K,
+ * 1 = tensor-core split-K, 2 = tensor-core persistent schedule (ignored where the
+ * variant does not take the shape); part_tokens: 0 = the planner's choice, else
+ * tokens per split-K partition (>= 32, rounded down to a multiple of 32).  The
+ * environment variables VT_ATTN_VARIANT (simt | mma | flat) and
+ * VT_ATTN_PART_TOKENS give the initial values and are read once. */
+int vt_attn_set_tuning(int variant, int part_tokens);
+
 /* What vt_decode_attn will do for this problem: tokens per split-K partition,
  * partitions per sequence the scratch is laid out for (> 1 means the merge
  * kernel runs too), and the kernel variant (0 = SIMT, 1 = tensor-core GQA).
@@ -414,11 +423,18 @@ int vt_all_reduce_emulated(vt_ar *const *ars, const void *const *ins, void *cons
  * file-scope __device__ array of VT_STATIC_SCRATCH_BYTES bytes that every GPU
  * holds from the moment it loads the library until the process exits.
  *
- * Same arguments and results as vt_decode_attn minus workspace / workspace_bytes;
- * outputs are identical to vt_decode_attn's for the same inputs.  Differences:
- *   - a problem whose scratch need exceeds VT_STATIC_SCRATCH_BYTES returns
- *     VT_ERR_TOO_LARGE and launches nothing (query group of 16, very large
- *     batch x kv-head counts, or the fp8 split-K path with long contexts);
+ * Same arguments and results as vt_decode_attn minus workspace / workspace_bytes.
+ * Differences:
+ *   - scratch need is checked against VT_STATIC_SCRATCH_BYTES.  The default
+ *     (persistent) schedule fits for every bf16 shape and for an fp8 cache with
+ *     query groups up to 8.  When it does not fit (fp8 with a query group of 16)
+ *     and num_splits is 0, the call falls back to the split-K schedule with 4, 2
+ *     or 1 partitions per sequence, whichever fits first: same result within the
+ *     library's parity tolerance, slower kernel.  If nothing fits (or the split
+ *     count the caller forced does not), it returns VT_ERR_TOO_LARGE and launches
+ *     nothing;
+ *   - when the default schedule fits, outputs are bit-identical to
+ *     vt_decode_attn's for the same inputs;
  *   - the call itself never allocates or frees: no cudaMalloc / cudaFree and no
  *     allocating library routine;
  *   - the FIRST call on each device resolves the array's device address
@@ -428,7 +444,7 @@ int vt_all_reduce_emulated(vt_ar *const *ars, const void *const *ins, void *cons
  *     contents (the ticket counters are cleared on every call).  Two calls that
  *     overlap on the GPU (different streams) race on it: serialise them;
  *   - the kernel status word of this buffer cannot be read back. */
-#define VT_STATIC_SCRATCH_BYTES (16u << 20)
+#define VT_STATIC_SCRATCH_BYTES (24u << 20)
 int vt_decode_attn_static(void *out, int64_t out_stride, const void *q, int64_t q_stride,
                           const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
                           const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len,

@@ -29,6 +29,15 @@ VARIANTS = {"vt_ref_bf16": BASE_FLAGS + ["-mavx512bf16"],
             "vt_ref_nobf16": BASE_FLAGS}
 
 
+def reference_root():
+    """The reference checkout: $GLAKE_REFERENCE, else a directory named "reference"
+    beside this repository; None when neither holds the GLakeServe sources."""
+    for cand in (os.environ.get("GLAKE_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "GLakeServe", "csrc", "cpu")):
+            return os.path.abspath(cand)
+    return None
+
+
 def build(reference_root, verbose=False):
     cpu_dir = os.path.join(reference_root, "GLakeServe", "csrc", "cpu")
     srcs = [os.path.join(HERE, "ref_shim.cpp"),
@@ -63,9 +72,11 @@ def build(reference_root, verbose=False):
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default=os.environ.get("GLAKE_REFERENCE", "/root/reference"))
+    ap.add_argument("--reference", default=reference_root())
     ap.add_argument("-v", "--verbose", action="store_true")
     a = ap.parse_args()
+    if not a.reference:
+        sys.exit("no reference checkout: pass --reference or set GLAKE_REFERENCE")
     for p in build(a.reference, a.verbose):
         print("built", p)
     sys.exit(0)

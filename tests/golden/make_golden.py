@@ -21,6 +21,10 @@ CPU paged_attention_v1 as a decode query of its own over the tokens it may see
 (context = its position + 1), which is what causal attention over prefix + new
 tokens means; the outputs are stored in query order.
 
+tests/synth.py:LONG_CASES are the same decode flow at the context lengths of the
+long-context, fp8 and tensor-parallel configurations (up to 32 768 tokens, which
+takes the reference's paged_attention_v2 and its 512-token partitions).
+
 Usage: python tests/golden/make_golden.py
 """
 import os
@@ -123,7 +127,7 @@ def run_prefill_case(name):
 
 
 if __name__ == "__main__":
-    for name in synth.GOLDEN_CASES:
+    for name in list(synth.GOLDEN_CASES) + list(synth.LONG_CASES):
         run_case(name)
     for name in synth.ROPE_CASES:
         run_rope_case(name)

@@ -48,8 +48,20 @@ GOLDEN_CASES = {
 }
 
 
+# Real-data cases at the context lengths of the long-context / fp8 / tensor-parallel
+# configurations (name -> (seed, lens, H, KVH)); goldens come from the reference's CPU
+# paged_attention_v2 (v1 up to 8192 tokens).  "fp8_ctx" is run with a bf16 cache by the
+# reference (it has no fp8 kernel) and with both cache types by the GPU tests.
+LONG_CASES = {
+    "long_gqa4_32k": (6, [16384, 32768, 20011, 29999], 32, 8),
+    "fp8_ctx_gqa4_8k": (7, [2048, 8192, 5000, 3333, 7777, 4097], 32, 8),
+    "share_tp8_16k": (8, [4096, 16384, 9001, 12345], 8, 1),
+    "share_tp4_16k": (9, [4099, 16384, 8192, 15000], 16, 2),
+}
+
+
 def golden_lens(name):
-    seed, lens, h, kvh = GOLDEN_CASES[name]
+    seed, lens, h, kvh = GOLDEN_CASES[name] if name in GOLDEN_CASES else LONG_CASES[name]
     if isinstance(lens, tuple):
         lens = uniform_lens(seed, *lens[1:])
     return seed, lens, h, kvh

@@ -118,6 +118,28 @@ def test_injected_driver_failure_rolls_back(pool, call, nth):
     assert lib.vt_seg_destroy(s) == 0
 
 
+def test_failed_unmap_poisons_the_segment_until_a_release_gets_through(pool):
+    """A cuMemUnmap that fails part-way through a release leaves some ranges cut back
+    and others not: no growth or row bookkeeping may succeed on that slot (a later
+    growth at the stale frontier would leave an unmapped hole that kernels would
+    read), and a second release or destroy finishes the job with every chunk back."""
+    st, s = seg_create(pool, 2, 16 * MiB)
+    assert st == 0 and lib.vt_seg_grow(s, 3 * CH) == 0 and free_chunks(pool) == 64 - 12
+    lib.vt_mock_fail_nth(b"cuMemUnmap", 3)                      # ranges 0 and 1 succeed, range 2 fails
+    assert lib.vt_seg_release(s, CH) == _lib.VT_ERR_DRIVER
+    assert free_chunks(pool) == 64 - 12 + 4                     # two ranges handed two chunks back each
+    assert lib.vt_seg_grow(s, 4 * CH) == _lib.VT_ERR_STATE
+    assert lib.vt_seg_grow_async(s, 1) == 0 and lib.vt_seg_wait(s, 1_000_000) == _lib.VT_ERR_STATE
+    out = (c_int64 * 1)()
+    segs = (c_void_p * 1)(s)
+    tb = (c_uint64 * 1)(8192)
+    assert lib.vt_extend_batch(segs, 1, None, tb, 8192, 1, 1000, out) == _lib.VT_ERR_STATE
+    assert lib.vt_seg_release(s, 0) == 0                        # a different watermark than the failed attempt
+    assert mapped(s) == 0 and free_chunks(pool) == 64
+    assert lib.vt_seg_grow(s, 2 * CH) == 0 and mapped(s) == 2 * CH   # usable again
+    assert lib.vt_seg_destroy(s) == 0 and free_chunks(pool) == 64
+
+
 def test_pool_create_failure_is_reported():
     lib.vt_use_mock_driver(1)
     lib.vt_mock_fail_nth(b"cuMemCreate", 5)

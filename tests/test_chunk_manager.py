@@ -73,6 +73,8 @@ def test_manager_drives_the_allocator_consistently():
                 n = rng.randint(1, 3000)
                 s.append_tokens(n)
                 if m.can_allocate(s) == cm.AllocStatus.OK and m.allocate(s):
+                    cm.apply_allocate(s, segs[s.slot])          # prompt + headroom mapped at admission
+                    assert segs[s.slot].actual_size == s.reserve_size
                     off = A.extend_kv_cache_batch(None, None, [s.slot], [n * row], [segs[s.slot]], [0], row, False)
                     assert off == [0]
                     live[s.slot] = [s, n]

@@ -1,0 +1,191 @@
+"""GPU parity at the context lengths the long-context, fp8 and tensor-parallel
+configurations really run at, on real N(0,1) data (not structured inputs), so that
+the running-max rescale and the cross-piece / cross-partition merges are exercised
+numerically over tens of thousands of tokens.
+
+Checkers: the committed golden vectors made by the reference's own CPU kernels
+(GLakeServe/csrc/cpu/attention.cpp:433-746, paged_attention_v2 with its 512-token
+partitions above 8192 tokens, v1 below), the C restatement, and — when the compiled
+reference kernels load on this host — those kernels run live.
+
+Tolerances: bf16 cache <= 2e-3 max-abs; fp8 cache <= 3e-2 against the bf16-cache
+result and <= 1e-2 against the fp8 restatement (the reference's own fp8 tolerance,
+GLakeServe/tests/kernels/test_attention.py:271-274); cache bytes bit-exact.
+"""
+import numpy as np
+import pytest
+import torch
+
+from tests import synth
+from tests.test_oracle import SCALE, load_golden
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def G():
+    from tests import gpu_util
+    gpu_util.ensure_pool()
+    return gpu_util
+
+
+@pytest.fixture
+def tuning():
+    from glake_b200 import ops
+    yield ops.set_attn_tuning
+    ops.set_attn_tuning("auto")
+
+
+def max_err(a, b):
+    return float((a.float() - b.float()).abs().max())
+
+
+# (planner override, forced split count)
+BF16_MODES = [("auto", 0), ("flat", 0), ("mma", 0), ("mma", 4), ("mma", 61), ("simt", 0), ("simt", 7)]
+
+
+@pytest.mark.parametrize("name", list(synth.LONG_CASES))
+def test_long_context_real_data_against_the_reference(G, oracle, tuning, name):
+    z, gold = load_golden(name)
+    seed, lens, h, kvh = synth.golden_lens(name)
+    q, k, v = synth.make_case(seed, lens, h, kvh)
+    assert synth.digest(q, k, v) == str(z["input_sha256"])
+    kv = G.GpuKV(k, v, kvh)
+    try:
+        rows_k = [kv.read_rows(i, "k") for i in range(len(lens))]
+        rows_v = [kv.read_rows(i, "v") for i in range(len(lens))]
+        assert synth.digest(rows_k, rows_v) == str(z["cache_sha256"]), "cache contents are not bit-exact"
+        del rows_k, rows_v
+        r = oracle.fill_ranges(k, v)
+        port = oracle.port_decode_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32), kvh, SCALE)
+        live = None
+        if oracle.load_ref() is not None:
+            live = oracle.ref_decode_attn(q, k, v, SCALE)
+        for mode, splits in BF16_MODES:
+            tuning(mode)
+            out = kv.attend(q, SCALE, num_splits=splits)
+            assert max_err(out, gold) <= 2e-3, (mode, splits, "golden", max_err(out, gold))
+            assert max_err(out, port) <= 2e-3, (mode, splits, "restatement", max_err(out, port))
+            if live is not None:
+                assert max_err(out, live) <= 2e-3, (mode, splits, "live reference", max_err(out, live))
+        tuning("auto")
+        out, lse = kv.attend(q, SCALE, return_lse=True)
+        _, plse = oracle.port_decode_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32), kvh,
+                                          SCALE, return_lse=True)
+        assert torch.allclose(lse, plse, atol=2e-3)
+    finally:
+        kv.close()
+
+
+@pytest.mark.parametrize("name", ["fp8_ctx_gqa4_8k", "share_tp8_16k"])
+def test_fp8_cache_at_full_context_with_scales_from_the_prefill_append(G, oracle, tuning, name):
+    """Scales are amax / 448 per kv head over the PREFILL rows (vt_kv_scales at the first
+    append), frozen; the decode step's row is quantised with them and saturates if larger."""
+    from glake_b200 import ops
+    _, gold16 = load_golden(name)
+    seed, lens, h, kvh = synth.golden_lens(name)
+    q, k, v = synth.make_case(seed, lens, h, kvh)
+    pre_k = torch.cat([x[:-1] for x in k])
+    pre_v = torch.cat([x[:-1] for x in v])
+    ks = ops.kv_scales(pre_k.cuda(), kvh, 128)
+    vs = ops.kv_scales(pre_v.cuda(), kvh, 128)
+    assert torch.equal(ks.cpu(), oracle.port_kv_scales(pre_k)) and torch.equal(vs.cpu(), oracle.port_kv_scales(pre_v))
+    kv8 = G.GpuKV(k, v, kvh, fp8=True, k_scale=ks, v_scale=vs)
+    try:
+        r8 = oracle.fill_ranges(k, v, k_scale=ks.cpu(), v_scale=vs.cpu())
+        for i, n in enumerate(lens):
+            assert torch.equal(kv8.read_rows(i, "k"), r8.k_rows(i, n, kvh, 128, fp8=True))
+            assert torch.equal(kv8.read_rows(i, "v"), r8.v_rows(i, n, kvh, 128, fp8=True))
+        port8 = oracle.port_decode_attn(q, r8, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32), kvh,
+                                        SCALE, ks.cpu(), vs.cpu())
+        for mode, splits in [("auto", 0), ("flat", 0), ("simt", 0), ("simt", 5)]:
+            tuning(mode)
+            o8 = kv8.attend(q, SCALE, num_splits=splits)
+            assert max_err(o8, gold16) <= 3e-2, (mode, splits, "vs bf16-cache reference", max_err(o8, gold16))
+            assert max_err(o8, port8) <= 1e-2, (mode, splits, "vs fp8 restatement", max_err(o8, port8))
+    finally:
+        kv8.close()
+
+
+@pytest.mark.parametrize("h,kvh,fp8", [(8, 1, False), (2, 2, False), (4, 2, False), (8, 1, True), (4, 2, True),
+                                        (8, 4, True)])
+def test_many_short_streams_per_cta(G, oracle, tuning, h, kvh, fp8):
+    """Around a thousand contexts of 1..150 tokens: every CTA of the persistent
+    schedule walks through several whole streams, each published to and merged
+    from the same scratch slot, with warps that own no merge item running ahead."""
+    from glake_b200 import ops
+    rs = np.random.RandomState(5150 + h + kvh)
+    lens = [int(x) for x in rs.randint(1, 151, size=1000)]
+    q, k, v = synth.make_case(900 + h + kvh, lens, h, kvh)
+    ks = vs = None
+    if fp8:
+        ks = ops.kv_scales(torch.cat(k).cuda(), kvh, 128)
+        vs = ops.kv_scales(torch.cat(v).cuda(), kvh, 128)
+    kv = G.GpuKV(k, v, kvh, fp8=fp8, k_scale=ks, v_scale=vs)
+    try:
+        tuning("flat")
+        outs = [kv.attend(q, SCALE) for _ in range(3)]
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), "results differ between identical calls"
+        sl = torch.tensor(lens, dtype=torch.int32)
+        if fp8:
+            r = oracle.fill_ranges(k, v, k_scale=ks.cpu(), v_scale=vs.cpu())
+            port = oracle.port_decode_attn(q, r, torch.arange(len(lens)), sl, kvh, SCALE, ks.cpu(), vs.cpu())
+            err = (outs[0].float() - port.float()).abs()
+            tol = torch.maximum(torch.full_like(err, 3e-2), port.float().abs() * 2.0 ** -6)
+        else:
+            r = oracle.fill_ranges(k, v)
+            port = oracle.port_decode_attn(q, r, torch.arange(len(lens)), sl, kvh, SCALE)
+            err = (outs[0].float() - port.float()).abs()
+            tol = torch.maximum(torch.full_like(err, 2e-3), port.float().abs() * 2.0 ** -7)
+        assert bool((err <= tol).all()), float((err - tol).max())
+    finally:
+        kv.close()
+
+
+def test_fp8_decode_runner_two_layers_with_overlap_requested(G, oracle):
+    """An fp8 cache takes append + attention as two launches per layer; asking the
+    runner for layer-to-layer overlap must not let the attention read its newest row
+    before the append wrote it."""
+    from glake_b200 import ops
+    from glake_b200.backend import DecodeRunner, VTensorAttentionImpl, VTensorCacheEngine, VTensorMetadata, prepare_step
+    h, kvh, layers = 8, 8, 2
+    lens0 = [300, 2, 1500, 65, 700, 129]
+    rs = np.random.RandomState(4242)
+    eng = VTensorCacheEngine(layers, kvh, 128, len(lens0), 2048, cache_dtype="fp8_e4m3")
+    impl = VTensorAttentionImpl(h, 128, SCALE, kvh, kv_cache_dtype="fp8_e4m3")
+    try:
+        pre = [n - 1 for n in lens0]
+        hist_k = [[synth.normal_bf16(rs, n, kvh, 128) for n in pre] for _ in range(layers)]
+        hist_v = [[synth.normal_bf16(rs, n, kvh, 128) for n in pre] for _ in range(layers)]
+        ks = torch.stack([ops.kv_scales(torch.cat(hist_k[l]).cuda(), kvh, 128) for l in range(layers)])
+        vs = torch.stack([ops.kv_scales(torch.cat(hist_v[l]).cuda(), kvh, 128) for l in range(layers)])
+        slots = list(range(len(lens0)))
+        meta = VTensorMetadata(slots, pre, kvh, 128, num_prefills=len(pre), kv_elem_size=1)
+        prepare_step(meta, eng)
+        for l in range(layers):
+            ops.reshape_and_cache(torch.cat(hist_k[l]).cuda(), torch.cat(hist_v[l]).cuda(), eng.k_cache_ptr[l],
+                                  eng.v_cache_ptr[l], meta.slot_m, meta.slot_mapping, meta.seq_lens_tensor,
+                                  meta.cache_seq_lens, max(pre), kvh, 128, "fp8_e4m3", ks[l], vs[l])
+        runner = DecodeRunner(eng, impl, len(lens0), host_io=False, k_scale=ks, v_scale=vs, overlap=True)
+        lens = list(pre)
+        for step in range(4):
+            lens = [n + 1 for n in lens]
+            q = synth.normal_bf16(rs, layers, len(lens), h * 128)
+            nk = synth.normal_bf16(rs, layers, len(lens), kvh * 128)
+            nv = synth.normal_bf16(rs, layers, len(lens), kvh * 128)
+            runner.q.copy_(q), runner.k.copy_(nk), runner.v.copy_(nv)
+            runner.step(VTensorMetadata(slots, lens, kvh, 128, num_decode_tokens=len(lens), kv_elem_size=1))
+            runner.synchronize()
+            for l in range(layers):
+                hist_k[l] = [torch.cat([a, b.view(1, kvh, 128)]) for a, b in zip(hist_k[l], nk[l])]
+                hist_v[l] = [torch.cat([a, b.view(1, kvh, 128)]) for a, b in zip(hist_v[l], nv[l])]
+                r = oracle.fill_ranges(hist_k[l], hist_v[l], k_scale=ks[l].cpu(), v_scale=vs[l].cpu())
+                port = oracle.port_decode_attn(q[l].view(len(lens), h, 128), r, torch.arange(len(lens)),
+                                               torch.tensor(lens, dtype=torch.int32), kvh, SCALE, ks[l].cpu(), vs[l].cpu())
+                got = runner.out[l].view(len(lens), h, 128).cpu()
+                err = (got.float() - port.float()).abs()
+                tol = torch.maximum(torch.full_like(err, 1e-2), port.float().abs() * 2.0 ** -6)
+                assert bool((err <= tol).all()), (step, l, float((err - tol).max()))
+        assert runner.status() == 0
+    finally:
+        eng.close()

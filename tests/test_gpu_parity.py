@@ -28,6 +28,17 @@ def close_2e3(a, b, ulp_slack=False):
     return not bool(bad.any()), float((af - bf).abs().max())
 
 
+@pytest.fixture
+def force_variant():
+    """force_variant(mode) overrides the planner's kernel choice for one test."""
+    from glake_b200 import ops
+
+    def force(mode):
+        ops.set_attn_tuning(mode)
+    yield force
+    ops.set_attn_tuning("auto")
+
+
 @pytest.fixture(scope="module")
 def G():
     from tests import gpu_util
@@ -60,11 +71,10 @@ def test_golden_cases_cache_bits_and_attention(G, oracle, name):
 @pytest.mark.parametrize("h,kvh", [(4, 4), (8, 4), (8, 2), (8, 1), (16, 1), (32, 8), (12, 12), (3, 3)])
 @pytest.mark.parametrize("mode", ["auto", "simt", "mma", "flat"])
 @pytest.mark.parametrize("splits", [0, 1, 3])
-def test_group_sizes_variants_and_forced_splits(G, oracle, monkeypatch, h, kvh, mode, splits):
+def test_group_sizes_variants_and_forced_splits(G, oracle, force_variant, h, kvh, mode, splits):
     """Every kernel variant (SIMT split-K, tensor-core split-K, tensor-core flat
     schedule) on every head-group shape, with and without forced partitions."""
-    if mode != "auto":
-        monkeypatch.setenv("VT_ATTN_VARIANT", mode)
+    force_variant(mode)
     if mode == "flat" and splits:
         pytest.skip("the flat schedule has no split count")
     lens = [1, 31, 32, 33, 700, 1300, 65, 64]
@@ -165,12 +175,11 @@ def test_append_strided_source_padding_and_growth_keeps_data(G, oracle):
 
 @pytest.mark.parametrize("h,kvh", [(8, 8), (32, 8), (8, 1), (16, 2), (16, 4), (16, 1), (3, 3)])
 @pytest.mark.parametrize("mode", ["auto", "simt"])
-def test_fp8_kv_cache(G, oracle, monkeypatch, h, kvh, mode):
+def test_fp8_kv_cache(G, oracle, force_variant, h, kvh, mode):
     """fp8 e4m3 cache on the tensor-core flat schedule (f16 MMAs) and on the SIMT
     split-K kernel, every head-group shape incl. the ones that pack several token
     rows into one bulk copy."""
-    if mode != "auto":
-        monkeypatch.setenv("VT_ATTN_VARIANT", mode)
+    force_variant(mode)
     lens = [520, 2100, 64, 1, 129]
     q, k, v = synth.make_case(40 + kvh, lens, h, kvh)
     from glake_b200 import ops
@@ -530,17 +539,6 @@ def test_prefill_tensor_core_path_rescales_and_edges(G, oracle, h, kvh, scale):
         assert ok, err
     finally:
         kv.close()
-
-
-def test_tcgen05_descriptor_probe():
-    """The one-tile probe behind vt_umma.cuh's descriptor encodings (K-major and MN-major
-    operands, 128-byte swizzle, TMEM accumulator) still matches its host reference."""
-    import subprocess
-    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "glake_b200", "csrc", "probe", "umma_tile")
-    if not os.path.isfile(exe):
-        pytest.skip("probe not built (make -C glake_b200/csrc probe)")
-    res = subprocess.run([exe], capture_output=True, text=True, timeout=120)
-    assert res.returncode == 0 and res.stdout.count("-> OK") == 3, res.stdout + res.stderr
 
 
 def test_prefill_full_size_engines_agree_and_normalise(G):

@@ -26,7 +26,7 @@ def one_ulp_close(a, b, atol):
     return bool(((af - bf).abs() <= torch.maximum(torch.full_like(af, atol), ulp)).all())
 
 
-@pytest.mark.parametrize("name", list(synth.GOLDEN_CASES))
+@pytest.mark.parametrize("name", list(synth.GOLDEN_CASES) + list(synth.LONG_CASES))
 def test_port_matches_golden(oracle, name):
     z, gold = load_golden(name)
     seed, lens, h, kvh = synth.golden_lens(name)
