@@ -76,6 +76,7 @@ def _load():
         "vt_append": (c_int, [vp, vp, c_int64, c_int64, vp, vp, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                               vp, vp, vp]),
         "vt_kv_scales": (c_int, [vp, c_int64, c_int, c_int, c_int, vp, vp]),
+        "vt_kv_widen": (c_int, [vp, vp, vp, vp, c_int, c_int, c_int, c_int, vp, vp, vp, vp, vp]),
         "vt_rope_append": (c_int, [vp, vp, c_int64, c_int, vp, vp, c_int64, c_int64, vp, c_int, c_int, vp, vp, vp, vp,
                                    vp, vp, c_int, c_int, c_int, c_int, c_int, vp, vp, ctypes.c_uint, vp]),
         "vt_ar_buffer_bytes": (c_int, [sz, POINTER(sz)]),
@@ -86,7 +87,7 @@ def _load():
         "vt_ar_ipc_close": (c_int, [vp]),
         "vt_ar_create": (c_int, [c_int, c_int, POINTER(vp), sz, c_int, POINTER(vp)]),
         "vt_ar_destroy": (c_int, [vp]),
-        "vt_ar_configure": (c_int, [vp, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong]),
+        "vt_ar_configure": (c_int, [vp, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong]),
         "vt_ar_status": (c_int, [vp, POINTER(ctypes.c_uint32)]),
         "vt_all_reduce": (c_int, [vp, vp, vp, sz, vp]),
         "vt_all_reduce_emulated": (c_int, [POINTER(vp), POINTER(vp), POINTER(vp), c_int, sz, vp]),

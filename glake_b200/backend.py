@@ -26,6 +26,24 @@ from .vmm_allocator.vmm_allocator import KV_cache
 PHY_GRAN = vmmAllocator.granularitySize
 
 
+class nvtx_range:
+    """NVTX range on the host timeline, as the reference puts around the allocator wait, the
+    growth requests and each layer's attention (GLakeServe/vllm/model_executor/models/llama.py:242-261,
+    :323-337); a no-op where CUDA is not initialised."""
+
+    def __init__(self, name):
+        self.name = name
+        self.on = torch.cuda.is_available() and torch.cuda.is_initialized()
+
+    def __enter__(self):
+        if self.on:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if self.on:
+            torch.cuda.nvtx.range_pop()
+
+
 def _round_up(x, m):
     return (x + m - 1) // m * m
 
@@ -127,11 +145,13 @@ def prepare_step_host(meta: VTensorMetadata, engine: VTensorCacheEngine):
     decode = meta.num_prefills == 0
     if decode:
         if vmmAllocator.query_cycle(slots):
-            vmmAllocator.wait_ready(slots)
+            with nvtx_range("sync phy memory"):
+                vmmAllocator.wait_ready(slots)
         kv_size_list = [kv_size] * len(slots)
-        for seg, slot_id in zip(segs, meta.extend_seq_list):
-            if slot_id != -1:
-                seg.eagerExtend(kv_size, slot_id)
+        with nvtx_range("eager_extend"):
+            for seg, slot_id in zip(segs, meta.extend_seq_list):
+                if slot_id != -1:
+                    seg.eagerExtend(kv_size, slot_id)
         rows = [1] * len(slots)
     else:
         rows = meta.query_lens if meta.query_lens else meta.seq_lens
@@ -182,24 +202,33 @@ class VTensorAttentionImpl:
                 kv_scale: float = 1.0, k_scale=None, v_scale=None, prefill_maps=None):
         """query ``[tokens, H*D]``, key/value ``[tokens, KVH*D]`` -> ``[tokens, H*D]``.
         ``prefill_maps``: the layer's tensor-map table (``VTensorCacheEngine.prefill_maps``),
-        used by the prompt branch when given."""
+        used by the prompt branch when given.  ``k_scale`` / ``v_scale``: the layer's per-kv-head
+        scales of an fp8 cache (``ops.kv_scales`` of the first prompt's rows, then frozen)."""
+        with nvtx_range("vtensor attention: prompt" if attn_metadata.num_prefills > 0 else "vtensor attention: decode"):
+            return self._forward(query, key, value, key_cache, value_cache, attn_metadata, k_scale, v_scale,
+                                 prefill_maps)
+
+    def _forward(self, query, key, value, key_cache, value_cache, attn_metadata, k_scale, v_scale, prefill_maps):
         query = query.view(-1, self.num_heads, self.head_size)
         key = key.view(-1, self.num_kv_heads, self.head_size)
         value = value.view(-1, self.num_kv_heads, self.head_size)
         m = attn_metadata
         if m.num_prefills > 0:
-            if self.kv_cache_dtype not in ("auto", "bf16", "bfloat16", None):
-                raise NotImplementedError("prompt attention over an fp8 cache is not implemented")
             layer = key_cache.layer_index
+            fp8 = self.kv_cache_dtype not in ("auto", "bf16", "bfloat16", None)
+            if fp8:
+                prefill_maps = None      # maps of the fp8 ranges do not apply: the kernels run on widened scratch
             # the new rows go into the ranges first (entry i: query_lens[i] rows from source row
             # cache_seq_lens[i]), then the new tokens attend over prefix + new tokens
             ops.reshape_and_cache(key, value, m.k_cache_segment_ptr_list[layer], m.v_cache_segment_ptr_list[layer],
                                   m.slot_m, m.slot_mapping, m.query_lens_tensor, m.cache_seq_lens,
-                                  max(m.max_query_len, 2), self.num_kv_heads, self.head_size)
+                                  max(m.max_query_len, 2), self.num_kv_heads, self.head_size, self.kv_cache_dtype,
+                                  k_scale, v_scale)
             output = torch.empty_like(query)
             ops.prefill_attention(output, query, key_cache.vmm_ptr, value_cache.vmm_ptr, self.num_kv_heads, self.scale,
                                   m.slot_mapping, m.seq_lens_tensor, m.query_lens_tensor, m.cache_seq_lens,
-                                  m.max_query_len, maps=prefill_maps)
+                                  m.max_query_len, maps=prefill_maps, kv_cache_dtype=self.kv_cache_dtype,
+                                  k_scale=k_scale, v_scale=v_scale)
             return output.view(-1, self.num_heads * self.head_size)
         # append + attention of the layer as one fused step (one kernel launch for a
         # bf16 cache); equivalent to ops.reshape_and_cache followed by ops.fwd_kvcache
@@ -292,11 +321,13 @@ class DecodeRunner:
             vs = self.v_scale[layer] if self.v_scale is not None else None
             if self.host_io and layer % self.io_group == 0:
                 main.wait_event(self.ev_in[layer])
+            torch.cuda.nvtx.range_push(f"layer {layer}: append + attention")
             ops.decode_step(self.out[layer].view(b, self.impl.num_heads, self.impl.head_size),
                             self.q[layer].view(b, self.impl.num_heads, self.impl.head_size), self.k[layer],
                             self.v[layer], kc.vmm_ptr, vc.vmm_ptr, self.d64[:b], self.d64[b:], self.d32[:b],
                             meta.max_seq_len, self.impl.num_kv_heads, self.impl.scale, self.impl.kv_cache_dtype,
                             ks, vs, overlap=self.overlap and layer > 0, workspace=self.workspace)
+            torch.cuda.nvtx.range_pop()
             if self.post_layer is not None:
                 self.post_layer(layer)
             if self.host_io and ((layer + 1) % self.io_group == 0 or layer == n_layers - 1):

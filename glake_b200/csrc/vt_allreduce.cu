@@ -33,6 +33,16 @@
 // into that buffer again only after it has seen this rank's data of call n + 1.  That
 // leaves one NVLink one-way latency plus a local poll on the critical path.
 //
+// Messages above that and up to 2 MiB take the same idea in two phases ("push2"): the
+// ranks scatter-reduce and then broadcast, both times by storing into the receiver's
+// sentinel-filled buffers.  CTA b's slice is cut into one sub-slice per rank; every
+// rank stores sub-slice r of its input into rank r's scatter buffer (slot = source
+// rank), polls its own scatter slots for its sub-slice from every source, sums them
+// in rank order, stores the sum into every rank's gather buffer, and finally polls
+// its own gather buffer for the other ranks' sums.  Per rank (world - 1) / world of the
+// message leaves over NVLink in each phase, and the critical path is two one-way
+// latencies plus local polls: no flag round trip, no peer loads.
+//
 // Every wait is bounded by wall time (%globaltimer); when it runs out the CTA sets
 // the status word, keeps signalling so that nobody else waits for it, and returns.
 // Peer data moves with plain loads and stores only (no multimem, no TMA).
@@ -54,15 +64,19 @@ constexpr size_t kArFlagBytes = 4096;                        // one flag array: 
 constexpr uint32_t kArTimedOut = 0xDEAD0A88u;
 constexpr size_t kPushBytes = 256u << 10;                    // largest message of the push path
 constexpr uint32_t kSentinel = 0x80008000u;                  // (-0.0, -0.0) in bf16: "not written yet"
+constexpr size_t kPush2Bytes = 2u << 20;                     // largest message of the two-phase push path
+// scatter area of one rotation: world regions of ceil(message / world) vectors plus per-CTA rounding slack
+constexpr size_t kPush2ScatterBytes = kPush2Bytes + kArMaxWorld * (kArMaxCtas + 16) * 16;
 
 struct ArDev {                                               // lives in local device memory
-  int rank, world, n_ctas, one_shot_vecs, push_vecs;
+  int rank, world, n_ctas, one_shot_vecs, push_vecs, push2_vecs;
   unsigned long long wait_ns;
   size_t max_bytes;
   char *peer[kArMaxWorld];                                   // shared buffer of every rank, as mapped here
   uint32_t *epoch;                                           // [n_ctas] call numbers (local)
   uint32_t *push_epoch;                                      // [n_ctas] number of push-path calls (local)
   uint32_t *push_prev;                                       // [n_ctas] vectors of the previous push-path call (local)
+  uint32_t *push2_epoch, *push2_prev;                        // the same two for the two-phase push path
   uint32_t *status;                                          // local
 };
 
@@ -84,6 +98,16 @@ __device__ __forceinline__ uint4 *result(char *buf, size_t max_bytes, int parity
 // push path: receive buffer t (0..2), slot of source rank r
 __device__ __forceinline__ uint4 *push_slot(char *buf, size_t max_bytes, int t, int r) {
   return reinterpret_cast<uint4 *>(buf + 2 * kArFlagBytes + 4 * max_bytes + (static_cast<size_t>(t) * kArMaxWorld + r) * kPushBytes);
+}
+
+// two-phase push path: scatter area of rotation t (regions by source rank inside), gather buffer of rotation t
+__device__ __forceinline__ uint4 *push2_scatter(char *buf, size_t max_bytes, int t) {
+  return reinterpret_cast<uint4 *>(buf + 2 * kArFlagBytes + 4 * max_bytes + 3 * kArMaxWorld * kPushBytes +
+                                   static_cast<size_t>(t) * kPush2ScatterBytes);
+}
+__device__ __forceinline__ uint4 *push2_gather(char *buf, size_t max_bytes, int t) {
+  return reinterpret_cast<uint4 *>(buf + 2 * kArFlagBytes + 4 * max_bytes + 3 * kArMaxWorld * kPushBytes +
+                                   3 * kPush2ScatterBytes + static_cast<size_t>(t) * kPush2Bytes);
 }
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
@@ -263,6 +287,122 @@ __device__ __forceinline__ void push_body(const ArDev &d, const uint4 *in, uint4
   }
 }
 
+__device__ __forceinline__ uint4 no_sentinel(uint4 x) {
+  x.x = x.x == kSentinel ? 0u : x.x; x.y = x.y == kSentinel ? 0u : x.y;
+  x.z = x.z == kSentinel ? 0u : x.z; x.w = x.w == kSentinel ? 0u : x.w;
+  return x;
+}
+__device__ __forceinline__ bool has_sentinel(const uint4 &x) {
+  return x.x == kSentinel || x.y == kSentinel || x.z == kSentinel || x.w == kSentinel;
+}
+// Re-reads *src until no word holds the sentinel; false when the wait ran out.
+__device__ __forceinline__ bool poll_vector(const uint4 *src, uint4 *x, unsigned long long wait_ns) {
+  if (!has_sentinel(*x)) return true;
+  const unsigned long long t0 = global_ns();
+  for (unsigned it = 0;; ++it) {
+    *x = ld_relaxed_sys(src);
+    if (!has_sentinel(*x)) return true;
+    if ((it & 63u) == 63u && global_ns() - t0 > wait_ns) return false;
+  }
+}
+
+// Geometry of one CTA's slice in the two-phase push path: slice [lo, hi) of the message,
+// q vectors per rank's sub-slice (the same q in every CTA, so that region offsets agree).
+struct Push2Geo {
+  int lo, hi, q, region;   // region = vectors per source region of the scatter area
+  __device__ __forceinline__ Push2Geo(int n_vec, int n_ctas, int world, int b) {
+    const int per = (n_vec + n_ctas - 1) / n_ctas;
+    lo = min(b * per, n_vec);
+    hi = min(lo + per, n_vec);
+    q = (per + world - 1) / world;
+    region = n_ctas * q;
+  }
+  __device__ __forceinline__ int sub_lo(int r) const { return min(lo + r * q, hi); }
+  __device__ __forceinline__ int sub_hi(int r) const { return min(sub_lo(r) + q, hi); }
+};
+
+template <int W>
+__device__ __forceinline__ void push2_body(const ArDev &d, const uint4 *in, uint4 *out, int n_vec, int *timed_out) {
+  const int b = blockIdx.x, me_r = d.rank;
+  const uint32_t e = d.push2_epoch[b] + 1;
+  const int n_prev = static_cast<int>(d.push2_prev[b]);
+  const int cur = e % 3, clr = (e + 2) % 3;                  // clr held the data of call e - 1 of this path
+  const Push2Geo g(n_vec, d.n_ctas, W, b);
+  char *me = d.peer[me_r];
+  // 1. scatter: sub-slice r of this rank's input into region `me_r` of rank r's scatter area
+  for (int i = threadIdx.x; i < g.hi - g.lo; i += kArThreads) {
+    const int r = i / g.q;
+    if (r != me_r)
+      push2_scatter(d.peer[r], d.max_bytes, cur)[me_r * g.region + b * g.q + (i - r * g.q)] = no_sentinel(in[g.lo + i]);
+  }
+  // 2. restore the sentinel where the previous call of this path landed in this rank's buffers
+  {
+    const Push2Geo p(n_prev, d.n_ctas, W, b);
+    const uint4 s4 = make_uint4(kSentinel, kSentinel, kSentinel, kSentinel);
+    const int mine = p.sub_hi(me_r) - p.sub_lo(me_r);
+    uint4 *sc = push2_scatter(me, d.max_bytes, clr);
+    for (int i = threadIdx.x; i < mine * W; i += kArThreads) {
+      const int r = i / max(mine, 1);
+      if (r != me_r) sc[r * p.region + b * p.q + (i - r * mine)] = s4;
+    }
+    uint4 *ga = push2_gather(me, d.max_bytes, clr);
+    for (int v = p.lo + threadIdx.x; v < p.hi; v += kArThreads) ga[v] = s4;
+  }
+  // 3. own sub-slice: wait for every source's vector (the data is the flag), sum in rank order,
+  //    hand the sum to every rank's gather buffer
+  bool ok = true;
+  const int s_lo = g.sub_lo(me_r), s_hi = g.sub_hi(me_r);
+  const uint4 *sc = push2_scatter(me, d.max_bytes, cur);
+  for (int v = s_lo + threadIdx.x; v < s_hi; v += kArThreads) {
+    uint4 x[W];
+#pragma unroll
+    for (int r = 0; r < W; ++r)
+      x[r] = r == me_r ? in[v] : ld_relaxed_sys(sc + r * g.region + b * g.q + (v - s_lo));
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < W; ++r) {
+      if (r != me_r) ok = poll_vector(sc + r * g.region + b * g.q + (v - s_lo), &x[r], d.wait_ns) && ok;
+      add8(acc, x[r]);
+    }
+    const uint4 sum = make_uint4(pack2(acc[0], acc[1]), pack2(acc[2], acc[3]), pack2(acc[4], acc[5]), pack2(acc[6], acc[7]));
+    const uint4 sent = no_sentinel(sum);                     // (-0, -0) travels as (+0, +0)
+#pragma unroll
+    for (int r = 0; r < W; ++r)
+      if (r != me_r) push2_gather(d.peer[r], d.max_bytes, cur)[v] = sent;
+    if (ok) out[v] = sent;
+  }
+  // 4. the other ranks' sums
+  {
+    const uint4 *ga = push2_gather(me, d.max_bytes, cur);
+    constexpr int U = 4;
+    const int own = s_hi - s_lo, rest = (g.hi - g.lo) - own;
+    for (int i0 = threadIdx.x; i0 < rest; i0 += kArThreads * U) {
+      uint4 x[U];
+      int vv[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int i = i0 + u * kArThreads;
+        vv[u] = g.lo + i + (g.lo + i >= s_lo ? own : 0);      // skip over the own sub-slice
+        if (i < rest) x[u] = ld_relaxed_sys(ga + vv[u]);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (i0 + u * kArThreads < rest) {
+          ok = poll_vector(ga + vv[u], &x[u], d.wait_ns) && ok;
+          if (ok) out[vv[u]] = x[u];
+        }
+      }
+    }
+  }
+  if (!ok) *timed_out = 1;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    d.push2_epoch[b] = e;
+    d.push2_prev[b] = static_cast<uint32_t>(n_vec);
+    if (*timed_out) atomicExch(d.status, kArTimedOut);
+  }
+}
+
 __global__ void __launch_bounds__(kArThreads) fill_words_kernel(uint32_t *p, size_t n, uint32_t value) {
   for (size_t i = blockIdx.x * static_cast<size_t>(kArThreads) + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * kArThreads)
     p[i] = value;
@@ -275,16 +415,18 @@ __global__ void __launch_bounds__(kArThreads, 2) all_reduce_kernel(const __grid_
   uint4 *out = static_cast<uint4 *>(L.out[blockIdx.y]);
   if (threadIdx.x == 0) timed_out = 0;
   __syncthreads();
-  const bool push = n_vec <= d.push_vecs;
+  const bool push = n_vec <= d.push_vecs, push2 = !push && n_vec <= d.push2_vecs && d.world > 1;
 #define VT_AR_CASE(W)                                              \
   case W:                                                          \
     if (push) push_body<W>(d, in, out, n_vec, &timed_out);         \
+    else if (push2) push2_body<W>(d, in, out, n_vec, &timed_out);  \
     else all_reduce_body<W>(d, in, out, n_vec, &timed_out);        \
     break;
   switch (d.world) {
     VT_AR_CASE(1) VT_AR_CASE(2) VT_AR_CASE(3) VT_AR_CASE(4) VT_AR_CASE(5) VT_AR_CASE(6) VT_AR_CASE(7)
     default:
       if (push) push_body<8>(d, in, out, n_vec, &timed_out);
+      else if (push2) push2_body<8>(d, in, out, n_vec, &timed_out);
       else all_reduce_body<8>(d, in, out, n_vec, &timed_out);
       break;
   }
@@ -301,7 +443,7 @@ struct vt_ar {
 };
 
 namespace {
-size_t push_bytes_total() { return 3 * vt::kArMaxWorld * vt::kPushBytes; }
+size_t push_bytes_total() { return 3 * vt::kArMaxWorld * vt::kPushBytes + 3 * vt::kPush2ScatterBytes + 3 * vt::kPush2Bytes; }
 size_t shared_bytes(size_t max_bytes) { return 2 * vt::kArFlagBytes + 4 * max_bytes + push_bytes_total(); }
 bool cuda_ok(cudaError_t e) { return e == cudaSuccess; }
 }  // namespace
@@ -356,8 +498,8 @@ int vt_ar_create(int rank, int world, void *const *peer_bufs, size_t max_bytes, 
   vt_ar *ar = new (std::nothrow) vt_ar();
   if (!ar) return VT_ERR_CUDA;
   if (!cuda_ok(cudaGetDevice(&ar->device)) ||
-      !cuda_ok(cudaMalloc(&ar->local, (3 * vt::kArMaxCtas + 1) * sizeof(uint32_t))) ||
-      !cuda_ok(cudaMemset(ar->local, 0, (3 * vt::kArMaxCtas + 1) * sizeof(uint32_t)))) {
+      !cuda_ok(cudaMalloc(&ar->local, (5 * vt::kArMaxCtas + 1) * sizeof(uint32_t))) ||
+      !cuda_ok(cudaMemset(ar->local, 0, (5 * vt::kArMaxCtas + 1) * sizeof(uint32_t)))) {
     cudaFree(ar->local);
     delete ar;
     return VT_ERR_CUDA;
@@ -374,7 +516,10 @@ int vt_ar_create(int rank, int world, void *const *peer_bufs, size_t max_bytes, 
   h.epoch = ar->local;
   h.push_epoch = ar->local + vt::kArMaxCtas;
   h.push_prev = ar->local + 2 * vt::kArMaxCtas;
-  h.status = ar->local + 3 * vt::kArMaxCtas;
+  h.push2_epoch = ar->local + 3 * vt::kArMaxCtas;
+  h.push2_prev = ar->local + 4 * vt::kArMaxCtas;
+  h.status = ar->local + 5 * vt::kArMaxCtas;
+  h.push2_vecs = static_cast<int>(vt::kPush2Bytes / 16);
   // the receive buffers of the push path start out as "nothing written" (own buffer only: every rank does its own)
   char *push0 = static_cast<char *>(peer_bufs[rank]) + 2 * vt::kArFlagBytes + 4 * max_bytes;
   vt::fill_words_kernel<<<64, vt::kArThreads>>>(reinterpret_cast<uint32_t *>(push0), push_bytes_total() / 4, vt::kSentinel);
@@ -394,8 +539,10 @@ int vt_ar_destroy(vt_ar *ar) {
   return VT_OK;
 }
 
-int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes, long long push_bytes) {
+int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes, long long push_bytes, long long push2_bytes) {
   if (!ar) return VT_ERR_INVALID;
+  if (push2_bytes >= 0)
+    ar->host.push2_vecs = static_cast<int>(std::min<long long>(push2_bytes, static_cast<long long>(vt::kPush2Bytes)) / 16);
   if (push_bytes >= 0)
     ar->host.push_vecs = static_cast<int>(std::min<long long>(push_bytes, static_cast<long long>(vt::kPushBytes)) / 16);
   if (wait_ns > 0) ar->host.wait_ns = static_cast<unsigned long long>(wait_ns);

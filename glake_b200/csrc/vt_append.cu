@@ -92,7 +92,47 @@ __global__ void __launch_bounds__(256) kv_scales_kernel(const __nv_bfloat16 *x, 
   }
 }
 
+// fp8 ranges -> dense bf16 rows: x = bf16(e4m3 * scale[kv_head]), the dequantisation of the
+// reference's scaled_convert (GLakeServe/csrc/quantization/fp8/nvidia/quant_utils.cuh:347-359).
+// grid: (entry, row blocks); one thread widens 16 bytes to 32.
+__global__ void __launch_bounds__(kAppendThreads) kv_widen_kernel(KvWidenParams p, int rows_per_cta) {
+  const int i = blockIdx.x;
+  const int n_rows = p.seq_lens[i];
+  const int t0 = blockIdx.y * rows_per_cta;
+  if (t0 >= n_rows) return;
+  const int64_t slot = p.slot_ids[i];
+  const int vec_per_row = p.kvh * kHeadDim / 16;
+  const int t1 = min(t0 + rows_per_cta, n_rows);
+#pragma unroll
+  for (int kv = 0; kv < 2; ++kv) {
+    const uint4 *src = reinterpret_cast<const uint4 *>(kv ? p.v_table[slot] : p.k_table[slot]);
+    uint4 *dst = reinterpret_cast<uint4 *>(kv ? p.v_out[i] : p.k_out[i]);
+    const float *scale = kv ? p.v_scale : p.k_scale;
+    for (int idx = t0 * vec_per_row + threadIdx.x; idx < t1 * vec_per_row; idx += kAppendThreads) {
+      const float sc = scale[(idx % vec_per_row) / (kHeadDim / 16)];
+      float f[16];
+      Unpack<true>::run(__ldg(src + idx), f);
+      uint32_t w[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        __nv_bfloat162 v = __floats2bfloat162_rn(f[2 * e] * sc, f[2 * e + 1] * sc);
+        w[e] = *reinterpret_cast<uint32_t *>(&v);
+      }
+      dst[2 * idx] = make_uint4(w[0], w[1], w[2], w[3]);
+      dst[2 * idx + 1] = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+  }
+}
+
 }  // namespace
+
+int launch_kv_widen(const KvWidenParams &p, int max_seq_len, cudaStream_t stream) {
+  if (p.batch == 0 || max_seq_len <= 0) return VT_OK;
+  constexpr int kRows = 32;
+  dim3 grid(p.batch, (max_seq_len + kRows - 1) / kRows);
+  kv_widen_kernel<<<grid, kAppendThreads, 0, stream>>>(p, kRows);
+  return cudaGetLastError() == cudaSuccess ? VT_OK : VT_ERR_CUDA;
+}
 
 int launch_append(const AppendParams &p, int kv_dtype, cudaStream_t stream) {
   if (p.batch == 0) return VT_OK;

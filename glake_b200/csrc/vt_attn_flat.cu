@@ -216,7 +216,10 @@ attn_flat_kernel(AttnParams p) {
         }
         const int t0 = tile * TILE_TOK;
         const int nt = min(TILE_TOK, seq_len - t0);
-        if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2u * nt * HS * kRowB);
+        // fp8 fused step: the newest token's row is quantised into the stage by the consumer
+        // warp that owns it, so this tile's copies bring one row less of K and of V
+        const int nt_copied = nt - ((kFp8 && fresh && t0 + nt == seq_len) ? 1 : 0);
+        if (lane == 0) mbar_arrive_expect_tx(full0 + 8 * s, 2u * nt_copied * HS * kRowB);
         __syncwarp();
         int rows = min(R, nt - grp * R);   // valid token rows of this lane's group
         if (rows > 0) {
@@ -224,7 +227,7 @@ attn_flat_kernel(AttnParams p) {
           if (fresh && t0 + grp * R + rows == seq_len) {
             // the newest token comes straight from this step's input row
             --rows;
-            bulk_g2s(dst + rows * HS * kRowB, fresh, HS * kRowB, full0 + 8 * s);
+            if (!kFp8) bulk_g2s(dst + rows * HS * kRowB, fresh, HS * kRowB, full0 + 8 * s);
           }
           if (rows > 0)
             bulk_g2s_hint(dst, base + static_cast<size_t>(t0 + grp * R) * tok_pitch, rows * HS * kRowB,
@@ -284,18 +287,40 @@ attn_flat_kernel(AttnParams p) {
       if (!failed && !mbar_wait(full0 + 8 * s, (it / kStages) & 1)) failed = true;
       if (failed) continue;
       const int tok0 = tile * TILE_TOK + rr;      // token of fragment row 0
-      if (!kFp8 && append_off >= 0 && (seq_len - 1 - tok0) % R == 0 && seq_len - 1 >= tok0 &&
-          seq_len - 1 < (tile + 1) * TILE_TOK) {
-        // Fused step: this warp holds the newest token's row of its kv head; make it
-        // part of the cache (8 bytes per lane for K and for V).
-        const unsigned char *row = smem + s * kStageB + ((seq_len - 1 - tok0) / R) * kPitch + row_off;
-        const size_t dst = static_cast<size_t>(append_off) + static_cast<size_t>(kv_head) * kRowB + lane * 8;
-        *reinterpret_cast<uint2 *>(append_k + dst) = *reinterpret_cast<const uint2 *>(row + lane * 8);
-        *reinterpret_cast<uint2 *>(append_v + dst) = *reinterpret_cast<const uint2 *>(row + kTileB + lane * 8);
+      const int n_rows = min(16, (seq_len - tok0 + R - 1) / R);
+      const bool newest_here = append_off >= 0 && (seq_len - 1 - tok0) % R == 0 && seq_len - 1 >= tok0 &&
+                               seq_len - 1 < (tile + 1) * TILE_TOK;
+      if (newest_here) {
+        // Fused step: this warp owns the newest token's row of its kv head; make it part of the cache.
+        unsigned char *row = smem + s * kStageB + ((seq_len - 1 - tok0) / R) * kPitch + row_off;
+        const size_t dst = static_cast<size_t>(append_off) + static_cast<size_t>(kv_head) * kRowB;
+        if constexpr (!kFp8) {
+          // the producer fetched it from the step's inputs: 8 bytes per lane for K and for V
+          *reinterpret_cast<uint2 *>(append_k + dst + lane * 8) = *reinterpret_cast<const uint2 *>(row + lane * 8);
+          *reinterpret_cast<uint2 *>(append_v + dst + lane * 8) = *reinterpret_cast<const uint2 *>(row + kTileB + lane * 8);
+        } else {
+          // quantise it here (4 elements per lane; true division, as the append kernel does, so the
+          // bytes equal sat(x / scale) exactly), into the stage for this step and into the range for good
+          const uint2 kx = __ldg(reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(p.new_key) +
+                                                                 pc.b * p.new_key_stride + kv_head * kHeadDim) + lane);
+          const uint2 vx = __ldg(reinterpret_cast<const uint2 *>(static_cast<const __nv_bfloat16 *>(p.new_value) +
+                                                                 pc.b * p.new_value_stride + kv_head * kHeadDim) + lane);
+          const float ks = p.k_scale[kv_head], vs = p.v_scale[kv_head];
+          const uint32_t kq = float2_to_e4m3x2(bf16_lo(kx.x) / ks, bf16_hi(kx.x) / ks) |
+                              (float2_to_e4m3x2(bf16_lo(kx.y) / ks, bf16_hi(kx.y) / ks) << 16);
+          const uint32_t vq = float2_to_e4m3x2(bf16_lo(vx.x) / vs, bf16_hi(vx.x) / vs) |
+                              (float2_to_e4m3x2(bf16_lo(vx.y) / vs, bf16_hi(vx.y) / vs) << 16);
+          *reinterpret_cast<uint32_t *>(row + lane * 4) = kq;
+          *reinterpret_cast<uint32_t *>(row + kTileB + lane * 4) = vq;
+          *reinterpret_cast<uint32_t *>(append_k + dst + lane * 4) = kq;
+          *reinterpret_cast<uint32_t *>(append_v + dst + lane * 4) = vq;
+          __syncwarp();
+        }
       }
-      if (tok0 < seq_len)
-        st.tile(ring0 + s * kStageB, smem + s * kStageB, k_off, v_off, row_off,
-                min(16, (seq_len - tok0 + R - 1) / R), sl2, lane);
+      if (tok0 < seq_len) st.tile(ring0 + s * kStageB, smem + s * kStageB, k_off, v_off, row_off, n_rows, sl2, lane);
+      // this warp's own stores into the stage (zeroed rows of a ragged tile, a quantised new row)
+      // must be ordered before the copy engine refills the stage
+      if (n_rows < 16 || (kFp8 && newest_here)) fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty0 + 8 * s);
     }

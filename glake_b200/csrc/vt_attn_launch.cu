@@ -173,6 +173,17 @@ int vt_kv_scales(const void *x, int64_t stride, int n_tokens, int kvh, int d, fl
   return vt::launch_kv_scales(x, stride, n_tokens, kvh, scale, static_cast<cudaStream_t>(stream));
 }
 
+int vt_kv_widen(const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
+                int batch, int kvh, int d, int max_seq_len, const float *k_scale, const float *v_scale,
+                const uint64_t *k_out, const uint64_t *v_out, void *stream) {
+  if (batch < 0 || kvh <= 0 || max_seq_len < 0) return VT_ERR_INVALID;
+  if (batch == 0) return VT_OK;
+  if (!k_table || !v_table || !slot_ids || !seq_lens || !k_scale || !v_scale || !k_out || !v_out) return VT_ERR_INVALID;
+  if (d != vt::kHeadDim) return VT_ERR_UNSUPPORTED;
+  vt::KvWidenParams p{k_table, v_table, slot_ids, seq_lens, k_out, v_out, batch, kvh, k_scale, v_scale};
+  return vt::launch_kv_widen(p, max_seq_len, static_cast<cudaStream_t>(stream));
+}
+
 int vt_decode_attn_workspace_bytes(int batch, int h, int d, int max_seq_len, size_t *bytes) {
   if (!bytes || batch < 0 || h <= 0 || max_seq_len < 0) return VT_ERR_INVALID;
   if (d != vt::kHeadDim) return VT_ERR_UNSUPPORTED;
@@ -207,7 +218,7 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
   p.batch = batch; p.h = h; p.kvh = kvh; p.scale = scale; p.k_scale = k_scale; p.v_scale = v_scale;
   p.lse = lse; p.part_tokens = plan.part_tokens; p.max_parts = plan.max_parts;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const bool fused = new_key && plan.variant == 2 && kv_dtype == VT_KV_BF16;
+  const bool fused = new_key && plan.variant == 2;   // the persistent kernel appends the step's rows itself
   if (new_key && !fused) {
     // no fused kernel for this shape / dtype: append first, then attend
     int st = vt_append(new_key, new_value, new_key_stride, new_value_stride, k_table, v_table, byte_off, slot_ids,

@@ -58,6 +58,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return false;
 }
 
+// Orders this thread's earlier generic-proxy accesses to shared memory before later
+// async-proxy (bulk copy) accesses to it.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // 1-D bulk async copy global -> this CTA's shared memory, completion counted in
 // bytes on an mbarrier.  Both addresses 16-byte aligned, bytes a multiple of 16.
 // No cluster multicast: the source is always this GPU's own memory and each CTA

@@ -40,6 +40,16 @@ struct AppendParams {
 int launch_append(const AppendParams &p, int kv_dtype, cudaStream_t stream);
 int launch_kv_scales(const void *x, int64_t stride, int n_tokens, int kvh, float *scale, cudaStream_t stream);
 
+struct KvWidenParams {
+  const uint64_t *k_table, *v_table;  // fp8 ranges
+  const int64_t *slot_ids;
+  const int32_t *seq_lens;            // rows to widen per entry
+  const uint64_t *k_out, *v_out;      // per entry: destination of its dense bf16 rows (16-byte aligned)
+  int batch, kvh;
+  const float *k_scale, *v_scale;
+};
+int launch_kv_widen(const KvWidenParams &p, int max_seq_len, cudaStream_t stream);
+
 struct AttnParams {
   void *out;  int64_t out_stride;     // bf16, elements per batch row
   const void *q; int64_t q_stride;

@@ -208,15 +208,16 @@ def fwd_kvcache(q, k_table_ptr, v_table_ptr, max_seq_len, num_kv_heads, batch, s
         raise RuntimeError("fwd_kvcache: q must be [B, S, H, D]")
     if q.shape[1] != 1:
         # prefix-extend form (xformers.py:362-385): S new tokens per sequence, causal over the range
-        if _kv_dtype(kv_cache_dtype) != VT_KV_BF16 or not causal:
-            raise RuntimeError("fwd_kvcache: seqlen_q > 1 needs a bf16 cache and causal=True")
+        if not causal:
+            raise RuntimeError("fwd_kvcache: seqlen_q > 1 needs causal=True")
         b, s, h, d = q.shape
         qc = q.contiguous().view(b * s, h, d)
         o = out if out is not None else torch.empty(b, s, h, d, dtype=q.dtype, device=q.device)
         q_lens = torch.full((b,), s, dtype=torch.int32, device=q.device)
         q_start = torch.arange(b, dtype=torch.int32, device=q.device) * s
         prefill_attention(o.view(b * s, h, d), qc, k_table_ptr, v_table_ptr, num_kv_heads, softmax_scale,
-                          slot_mapping, seq_lens, q_lens, q_start, s)
+                          slot_mapping, seq_lens, q_lens, q_start, s, kv_cache_dtype=kv_cache_dtype, k_scale=k_scale,
+                          v_scale=v_scale)
         return o, None
     b, _, h, d = q.shape
     q3 = q.view(b, h, d) if q.is_contiguous() else q[:, 0]
@@ -257,9 +258,9 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
 
 
 def step_is_fused(kv_cache_dtype):
-    """Whether decode_step on the persistent schedule is ONE launch (the attention kernel
-    appends the new rows itself) for this cache type; otherwise an append kernel runs first."""
-    return _kv_dtype(kv_cache_dtype) == VT_KV_BF16
+    """Whether decode_step on the persistent schedule is ONE launch for this cache type: the
+    attention kernel appends the new rows itself (bf16: copied, fp8: quantised on the way)."""
+    return _kv_dtype(kv_cache_dtype) in (VT_KV_BF16, VT_KV_FP8_E4M3)
 
 
 def prefill_tma_supported(num_kv_heads):
@@ -283,17 +284,60 @@ def prefill_maps(k_bases, v_bases, num_kv_heads, head_size, max_tokens, device):
     return host[off: off + n * 256].to(device)
 
 
+def widen_fp8_ranges(key_cache, value_cache, num_kv_heads, head_size, slot_mapping, seq_lens, k_scale, v_scale,
+                     pad_rows=64):
+    """Dense bf16 copies of the slots' fp8 rows for the prompt kernels: returns
+    (k_bases, v_bases, holder) where ``k_bases`` / ``v_bases`` are int64 device tensors
+    of one scratch range address per batch entry (usable as pointer tables with slot ids
+    0..B-1) and ``holder`` keeps the scratch alive.  Every entry's range is padded to a
+    multiple of ``pad_rows`` rows so that whole-tile fetches at its ragged end stay
+    inside the buffer.  Synchronises once to learn the context lengths."""
+    lens = [int(x) for x in seq_lens.tolist()]
+    row = num_kv_heads * head_size
+    padded = [(n + pad_rows - 1) // pad_rows * pad_rows + pad_rows for n in lens]
+    total = sum(padded)
+    dev = seq_lens.device
+    buf = torch.zeros(2, max(total, 1), row, dtype=torch.bfloat16, device=dev)
+    starts, acc = [], 0
+    for n in padded:
+        starts.append(acc)
+        acc += n
+    kb = torch.tensor([buf[0].data_ptr() + s * row * 2 for s in starts], dtype=torch.int64, device=dev)
+    vb = torch.tensor([buf[1].data_ptr() + s * row * 2 for s in starts], dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.vt_kv_widen(c_void_p(int(key_cache)), c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens),
+                              len(lens), num_kv_heads, head_size, max(lens) if lens else 0, _ptr(k_scale), _ptr(v_scale),
+                              _ptr(kb), _ptr(vb), _stream()), "vt_kv_widen")
+    return kb, vb, (buf, padded)
+
+
 def prefill_attention(out, query, key_cache, value_cache, num_kv_heads, scale, slot_mapping, seq_lens, q_lens,
-                      q_start, max_q_len, maps=None):
+                      q_start, max_q_len, maps=None, kv_cache_dtype="auto", k_scale=None, v_scale=None):
     """Causal attention of the new tokens over the slots' whole ranges (the new rows
     already appended with ``reshape_and_cache``).  query/out ``[tokens, H, D]`` bf16,
     ``key_cache`` / ``value_cache`` the pointer-table addresses (ints), ``seq_lens``
     the contexts including the new tokens, ``q_lens`` / ``q_start`` int32 per entry.
-    With ``maps`` (from :func:`prefill_maps`) K/V tiles are fetched by TMA tensor copies."""
+    With ``maps`` (from :func:`prefill_maps`) K/V tiles are fetched by TMA tensor copies.
+    An fp8 e4m3 cache (``kv_cache_dtype``, per-kv-head ``k_scale`` / ``v_scale``) is first
+    widened into bf16 scratch ranges (:func:`widen_fp8_ranges`), over which the same
+    kernels run, with tensor maps of the scratch where the head count allows."""
     _require_cuda(out, query, slot_mapping, seq_lens, q_lens, q_start, maps)
     if query.dtype != torch.bfloat16:
         raise RuntimeError("prefill_attention: bf16 only")
     n, num_heads, head_size = query.shape
+    holder = None
+    if _kv_dtype(kv_cache_dtype) == VT_KV_FP8_E4M3:
+        if k_scale is None or v_scale is None:
+            raise RuntimeError("prefill_attention: an fp8 cache needs k_scale and v_scale")
+        kb, vb, holder = widen_fp8_ranges(key_cache, value_cache, num_kv_heads, head_size, slot_mapping, seq_lens,
+                                          k_scale, v_scale)
+        batch = slot_mapping.numel()
+        key_cache, value_cache = kb.data_ptr(), vb.data_ptr()
+        slot_mapping = torch.arange(batch, dtype=torch.int64, device=query.device)
+        maps = None
+        if prefill_tma_supported(num_kv_heads):
+            maps = prefill_maps(kb.tolist(), vb.tolist(), num_kv_heads, head_size, max(holder[1]), query.device)
+        holder = (holder, kb, vb, slot_mapping, maps)
     args = (_ptr(out), out.stride(0), _ptr(query), query.stride(0), c_void_p(int(key_cache)),
             c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens), _ptr(q_lens),
             _ptr(q_start), slot_mapping.numel(), num_heads, num_kv_heads, head_size,
@@ -303,6 +347,10 @@ def prefill_attention(out, query, key_cache, value_cache, num_kv_heads, scale, s
             check(lib.vt_prefill_attn(*args, _stream()), "vt_prefill_attn")
         else:
             check(lib.vt_prefill_attn_tma(*args, _ptr(maps), _stream()), "vt_prefill_attn_tma")
+    if holder is not None:
+        # the scratch must outlive the kernels queued above: torch's allocator reuses a freed
+        # block only in stream order on the stream that allocated it, which is this one
+        del holder
 
 
 def attn_plan(batch, num_heads, num_kv_heads, max_seq_len, kv_cache_dtype="auto", num_splits=0):

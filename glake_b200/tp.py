@@ -142,9 +142,11 @@ class PeerAllReduce:
             self._check(self._lib.vt_ar_status(self._ar, ctypes.byref(st)), "vt_ar_status")
         return st.value
 
-    def configure(self, wait_ns=0, one_shot_bytes=-1, push_bytes=-1):
+    def configure(self, wait_ns=0, one_shot_bytes=-1, push_bytes=-1, push2_bytes=-1):
+        """Wait limit and the size thresholds of the four paths (see vt_ar_configure); -1 keeps a value."""
         with torch.cuda.device(self.device):
-            self._check(self._lib.vt_ar_configure(self._ar, wait_ns, one_shot_bytes, push_bytes), "vt_ar_configure")
+            self._check(self._lib.vt_ar_configure(self._ar, wait_ns, one_shot_bytes, push_bytes, push2_bytes),
+                        "vt_ar_configure")
 
     def close(self):
         if self._ar:

@@ -194,6 +194,19 @@ int vt_append(const void *key, const void *value, int64_t key_stride, int64_t va
 int vt_kv_scales(const void *x, int64_t stride, int n_tokens, int kvh, int d, float *scale,
                  void *stream);
 
+/* Widens fp8 e4m3 ranges into dense bf16 rows, x = bf16(e4m3 * scale[kv_head]): the
+ * dequantising direction of the reference's scaled_convert
+ * (GLakeServe/csrc/quantization/fp8/nvidia/quant_utils.cuh:347-359).  Entry i's first
+ * seq_lens[i] rows of K (and V) go to the device address k_out[i] (v_out[i]),
+ * 16-byte aligned, row = kvh * 128 bf16, token-major like the ranges themselves.
+ * This is how prompt / prefix-extend attention runs over an fp8 cache: the rows are
+ * widened into scratch ranges once and the bf16 tensor-core prefill kernels
+ * (vt_prefill_attn / vt_prefill_attn_tma) run on those; the extra traffic, 3 bytes
+ * per cache byte, is small next to the attention's flops. */
+int vt_kv_widen(const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids, const int32_t *seq_lens,
+                int batch, int kvh, int d, int max_seq_len, const float *k_scale, const float *v_scale,
+                const uint64_t *k_out, const uint64_t *v_out, void *stream);
+
 /* ---- decode attention -------------------------------------------------- */
 /* Scratch bytes vt_decode_attn needs for this problem size (max_seq_len is an
  * upper bound of every seq_lens entry).  The scratch holds the split-K partial
@@ -388,8 +401,12 @@ int vt_fused_add_rms_norm(void *input, void *residual, const void *weight, float
  *                        default 6 MiB / (world - 1); two ranks are always one-shot);
  *                        the message size up to which the flag-free push path is
  *                        used (< 0 keeps it, 0 disables it; default and maximum
- *                        256 KiB).  On the push path an input word holding two
- *                        negative zeros is summed as two positive zeros.
+ *                        256 KiB); the message size up to which larger messages
+ *                        take the two-phase push path (scatter-reduce, then
+ *                        broadcast, both by stores into sentinel-filled receive
+ *                        buffers; < 0 keeps it, 0 disables it; default and maximum
+ *                        2 MiB).  On the push paths an input word (or a sum) holding
+ *                        two negative zeros travels as two positive zeros.
  *   vt_all_reduce_emulated   runs all `world` ranks of one call as ONE cooperative
  *                        launch on a single GPU (every vt_ar created on that GPU
  *                        with the same peer_bufs): the way to exercise the protocol
@@ -404,7 +421,8 @@ int vt_ar_ipc_open(const unsigned char handle[64], void **buf);
 int vt_ar_ipc_close(void *buf);
 int vt_ar_create(int rank, int world, void *const *peer_bufs, size_t max_bytes, int n_ctas, vt_ar **out);
 int vt_ar_destroy(vt_ar *ar);
-int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes, long long push_bytes);
+int vt_ar_configure(vt_ar *ar, long long wait_ns, long long one_shot_bytes, long long push_bytes,
+                    long long push2_bytes);
 int vt_ar_status(vt_ar *ar, uint32_t *status);
 int vt_all_reduce(vt_ar *ar, const void *in, void *out, size_t n_elems, void *stream);
 int vt_all_reduce_emulated(vt_ar *const *ars, const void *const *ins, void *const *outs, int world,

@@ -42,7 +42,8 @@ def test_norm_argument_checks():
 def test_all_reduce_argument_checks():
     need = ctypes.c_size_t()
     assert lib.vt_ar_buffer_bytes(1 << 20, ctypes.byref(need)) == 0
-    assert need.value == 2 * 4096 + 4 * (1 << 20) + 3 * 8 * (256 << 10)      # flags, 2 staging + 2 result copies, push buffers
+    push2 = 3 * ((2 << 20) + 8 * (64 + 16) * 16) + 3 * (2 << 20)             # two-phase push: 3 scatter areas + 3 gather buffers
+    assert need.value == 2 * 4096 + 4 * (1 << 20) + 3 * 8 * (256 << 10) + push2   # flags, 2 staging + 2 result copies, push buffers
     assert lib.vt_ar_buffer_bytes(1000, ctypes.byref(need)) == VT_ERR_INVALID          # not a multiple of 256
     out = P()
     peers = (P * 9)(*[A16] * 9)

@@ -66,8 +66,8 @@ def test_emulated_ranks_match_the_oracle(oracle, world):
     torch.zeros(1, device="cuda")
     E = Emulated(world)
     try:
-        for a in E.ars:                                    # two-shot above 128 KiB, whatever the world size
-            E.check(E.lib.vt_ar_configure(a, 0, 128 << 10, -1), "vt_ar_configure")
+        for a in E.ars:                                    # two-shot above 128 KiB, whatever the world size; no two-phase push
+            E.check(E.lib.vt_ar_configure(a, 0, 128 << 10, -1, 0), "vt_ar_configure")
         # one-shot sizes, two-shot sizes, ragged vector counts, consecutive calls on both parities
         for call, n in enumerate([8, 8 * 37, 4096, 65536, 65536 + 8 * 5, 1 << 19, (1 << 19) + 8 * 123, 1 << 20, 8 * 3,
                                   1 << 20, 1 << 20]):
@@ -111,13 +111,45 @@ def test_emulated_push_path_buffer_rotation(oracle, world):
         assert all(E.status(r) == 0 for r in range(world))
         # the same messages with the push path switched off give the same values
         for a in E.ars:
-            E.check(E.lib.vt_ar_configure(a, 0, -1, 0), "vt_ar_configure")
+            E.check(E.lib.vt_ar_configure(a, 0, -1, 0, 0), "vt_ar_configure")
         ins = _inputs(77, world, 4096)
         d_in = [t.cuda() for t in ins]
         outs = [torch.empty_like(t) for t in d_in]
         assert E.run(d_in, outs) == 0
         torch.cuda.synchronize()
         assert all(torch.equal(o.cpu(), oracle.port_all_reduce(ins)) for o in outs)
+    finally:
+        E.close()
+
+
+@pytest.mark.parametrize("world,n_ctas", [(2, 16), (3, 16), (8, 16), (8, 32)])
+def test_emulated_two_phase_push_path(oracle, world, n_ctas):
+    """Messages between 256 KiB and 2 MiB: scatter-reduce then broadcast through
+    sentinel-filled buffers.  Sizes change from call to call (the restored ranges are the
+    previous call's), vector counts that do not divide by CTAs x ranks, calls of the other
+    paths in between, in-place calls, and inputs / sums that hit the sentinel's bit pattern."""
+    E = Emulated(world, n_ctas=n_ctas)
+    try:
+        sizes = [1 << 19, 1 << 20, (1 << 18) + 8 * 7, 8, 1 << 19, (1 << 19) + 8 * 1001, 1 << 20, 32768, 1 << 20,
+                 (1 << 17) + 8, 1 << 19, 1 << 19, 1 << 19]
+        for call, n in enumerate(sizes):
+            ins = _inputs(9000 + 10 * world + call, world, n)
+            for t in ins:
+                t[8:10] = -0.0                                        # every rank sends the sentinel pattern there
+                t[12] = -0.0
+            ins[0][16:18] = 1.5                                       # ... and here values cancel to zero next to negative zeros
+            ins[1][16:18] = -1.5
+            for t in ins[2:]:
+                t[16:18] = -0.0
+            want = oracle.port_all_reduce(ins)
+            d_in = [t.cuda() for t in ins]
+            d_out = [torch.empty_like(t) for t in d_in] if call % 3 else d_in
+            assert E.run(d_in, d_out) == 0
+            torch.cuda.synchronize()
+            for r in range(world):
+                got = d_out[r].cpu()
+                assert torch.equal(got.float(), want.float()), f"call {call} n {n} rank {r}"   # == treats -0 and +0 alike
+        assert all(E.status(r) == 0 for r in range(world))
     finally:
         E.close()
 
@@ -131,7 +163,7 @@ def test_emulated_forced_modes_agree(oracle):
         d_in = [t.cuda() for t in ins]
         for one_shot_bytes in (1 << 30, 0):
             for a in E.ars:
-                E.check(E.lib.vt_ar_configure(a, 0, one_shot_bytes, -1), "vt_ar_configure")
+                E.check(E.lib.vt_ar_configure(a, 0, one_shot_bytes, -1, 0), "vt_ar_configure")
             outs = [torch.empty_like(t) for t in d_in]
             assert E.run(d_in, outs) == 0
             torch.cuda.synchronize()
@@ -147,7 +179,7 @@ def test_a_missing_peer_ends_in_a_status_not_a_hang():
     from glake_b200._lib import VT_ERR_TOO_LARGE, VT_ERR_UNSUPPORTED
     E = Emulated(2, max_bytes=1 << 16)
     try:
-        E.check(E.lib.vt_ar_configure(E.ars[0], 2_000_000, -1, -1), "vt_ar_configure")       # 2 ms
+        E.check(E.lib.vt_ar_configure(E.ars[0], 2_000_000, -1, -1, -1), "vt_ar_configure")       # 2 ms
         x = torch.ones(1024, dtype=torch.bfloat16, device="cuda")
         y = torch.empty_like(x)
         stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -189,6 +221,12 @@ def _rank_main(rank, world, port, ret):
             want = O.port_all_reduce(ins)
             out = tp.tensor_model_parallel_all_reduce(ins[rank].cuda())
             ok = ok and torch.equal(out.cpu(), want)
+        comm.configure(push2_bytes=0)                      # the same large messages through the flag paths
+        for call, n in enumerate([1 << 19, 1 << 20, 1 << 19]):
+            ins = _inputs(950 + call, world, n)
+            out = tp.tensor_model_parallel_all_reduce(ins[rank].cuda())
+            ok = ok and torch.equal(out.cpu(), O.port_all_reduce(ins))
+        comm.configure(push2_bytes=2 << 20)
         # a captured sequence of calls replays correctly with new inputs
         x = torch.zeros(1 << 16, dtype=torch.bfloat16, device="cuda")
         y = torch.empty_like(x)

@@ -189,3 +189,57 @@ def test_fp8_decode_runner_two_layers_with_overlap_requested(G, oracle):
         assert runner.status() == 0
     finally:
         eng.close()
+
+
+@pytest.mark.parametrize("h,kvh", [(8, 2), (8, 8), (6, 3)])
+def test_backend_prompt_extend_decode_over_an_fp8_cache(G, oracle, h, kvh):
+    """The backend binding with an fp8 cache end to end: a prompt (scales = amax / 448 of
+    its rows, computed at that first append and frozen), a prefix-extend step, then decode
+    steps, two layers.  The prompt kernels run over widened scratch ranges; every phase is
+    compared with the fp8 restatement (which dequantises to bf16 exactly as the widening
+    does) and the cache bytes with its bytes."""
+    from glake_b200 import ops
+    from glake_b200.backend import VTensorAttentionImpl, VTensorCacheEngine, VTensorMetadata, prepare_step
+    layers = 2
+    eng = VTensorCacheEngine(layers, kvh, 128, 4, 2048, cache_dtype="fp8_e4m3")
+    impl = VTensorAttentionImpl(h, 128, SCALE, kvh, kv_cache_dtype="fp8_e4m3")
+    rs = np.random.RandomState(79 + kvh)
+    slots, ctx = [1, 2], [0, 0]
+    hist_k = [[torch.empty(0, kvh, 128, dtype=torch.bfloat16) for _ in slots] for _ in range(layers)]
+    hist_v = [[torch.empty(0, kvh, 128, dtype=torch.bfloat16) for _ in slots] for _ in range(layers)]
+    scales = [None] * layers
+    try:
+        for phase, new in enumerate([[300, 77], [50, 200], [1, 1], [1, 1]]):
+            decode = phase >= 2
+            ctx = [a + b for a, b in zip(ctx, new)]
+            if decode:
+                meta = VTensorMetadata(slots, ctx, kvh, 128, num_decode_tokens=2, kv_elem_size=1)
+            else:
+                meta = VTensorMetadata(slots, ctx, kvh, 128, num_prefills=2, query_lens=new, kv_elem_size=1)
+            prepare_step(meta, eng)
+            n, starts = sum(new), [0, new[0]]
+            for layer in range(layers):
+                q = synth.normal_bf16(rs, n, h * 128)
+                kk = synth.normal_bf16(rs, n, kvh * 128)
+                vv = synth.normal_bf16(rs, n, kvh * 128)
+                if scales[layer] is None:
+                    scales[layer] = (ops.kv_scales(kk.cuda(), kvh, 128), ops.kv_scales(vv.cuda(), kvh, 128))
+                ks, vs = scales[layer]
+                kc, vc = eng.gpu_cache[layer]
+                out = impl.forward(q.cuda(), kk.cuda(), vv.cuda(), kc, vc, meta, k_scale=ks, v_scale=vs).cpu()
+                for i in range(2):
+                    rows = slice(starts[i], starts[i] + new[i])
+                    hist_k[layer][i] = torch.cat([hist_k[layer][i], kk[rows].view(-1, kvh, 128)])
+                    hist_v[layer][i] = torch.cat([hist_v[layer][i], vv[rows].view(-1, kvh, 128)])
+                r = oracle.fill_ranges(hist_k[layer], hist_v[layer], k_scale=ks.cpu(), v_scale=vs.cpu())
+                port = oracle.port_prefill_attn(q.view(n, h, 128), r, torch.arange(2), torch.tensor(ctx, dtype=torch.int32),
+                                                torch.tensor(new, dtype=torch.int32), torch.tensor(starts, dtype=torch.int32),
+                                                kvh, SCALE, ks.cpu(), vs.cpu())
+                err = (out.view(n, h, 128).float() - port.float()).abs()
+                # prompt phases: same dequantised values as the restatement -> the bf16 tolerance (one ulp
+                # where short contexts make outputs O(1)); decode phases: the fp8 tolerance of the decode kernel
+                base = 1e-2 if decode else 2e-3
+                tol = torch.maximum(torch.full_like(err, base), port.float().abs() * (2.0 ** -6 if decode else 2.0 ** -7))
+                assert bool((err <= tol).all()), (phase, layer, float((err - tol).max()))
+    finally:
+        eng.close()

@@ -208,7 +208,8 @@ def test_fp8_kv_cache(G, oracle, force_variant, h, kvh, mode):
 
 
 @pytest.mark.parametrize("h,kvh,fp8", [(8, 1, False), (8, 2, False), (8, 4, False), (32, 32, False), (16, 1, False),
-                                        (3, 3, False), (8, 8, True)])
+                                        (3, 3, False), (8, 8, True), (8, 1, True), (4, 2, True), (16, 4, True),
+                                        (16, 1, True), (3, 3, True)])
 def test_fused_decode_step_appends_and_attends(G, oracle, h, kvh, fp8):
     """vt_decode_step = append + attention in one call (one launch for bf16): the
     cache must hold the new rows bit for bit afterwards and the output must match
@@ -244,6 +245,7 @@ def test_fused_decode_step_appends_and_attends(G, oracle, h, kvh, fp8):
                 r = oracle.fill_ranges(k, v, k_scale=ks.cpu(), v_scale=vs.cpu())
                 for i, n in enumerate(lens):
                     assert torch.equal(kv.read_rows(i, "k"), r.k_rows(i, n, kvh, 128, fp8=True))
+                    assert torch.equal(kv.read_rows(i, "v"), r.v_rows(i, n, kvh, 128, fp8=True))
                 port = oracle.port_decode_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32),
                                                kvh, SCALE, ks.cpu(), vs.cpu())
                 # the reference's own fp8 tolerance, or two bf16 ulps where the short
