@@ -423,7 +423,9 @@ def op_record(name, seed, steps, peak, with_cpu=False):
         job = Job(name, seed, 0, 1, steps + 8)
         try:
             r = job.runner("op", overlap=False)
-            ms, attn_b, app_b, launches, _ = timed(job, r, steps, 3, 1)
+            sampler = ClockSampler(job.dev.index)
+            ms, attn_b, app_b, launches, _ = timed(job, r, steps, 3, 1, sampler)
+            clocks = sampler.stop()
             calls = steps * job.layers
             from glake_b200 import ops
             _, parts, variant = ops.attn_plan(job.b, job.h, job.kvh, max(job.lens), job.dtype)
@@ -434,7 +436,8 @@ def op_record(name, seed, steps, peak, with_cpu=False):
                    "kernel": ["simt split-k", "tensor-core split-k", "tensor-core flat persistent"][variant]
                              + (", fused append" if ops.step_is_fused(job.dtype) else ", separate append kernel"),
                    "gpu_launches": launches, "kernel_status": job.kernel_status(),
-                   "how": "CUDA graph replays back to back, CUDA events, contexts grow by one token per call"}
+                   "how": "CUDA graph replays back to back, CUDA events, contexts grow by one token per call",
+                   "clocks": {"sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}}
             if job.layers > 1:
                 rec["l2"] = f"{job.layers} independent copies of the ranges cycled, so no call finds its KV in L2"
             if job.fp8:
@@ -456,14 +459,17 @@ def share_record(name, seed, steps, warmup, peak):
         job = Job(name, seed, 0, 1, steps + warmup + 8)
         try:
             r = job.runner("share")
-            ms, attn_b, app_b, launches, _ = timed(job, r, steps, warmup, 1)
+            sampler = ClockSampler(job.dev.index)
+            ms, attn_b, app_b, launches, _ = timed(job, r, steps, warmup, 1, sampler)
+            clocks = sampler.stop()
             alone_ms = job.time_attention_only()
             per_launch, _ = algorithmic_bytes(job.lens, 1, job.h, job.kvh, job.e)
             alone = per_launch / (alone_ms * 1e-3) / 1e9
             return {"workload": WORKLOAD_TEXT[name], "ms_per_step": round(ms / steps, 4), "GB/s": rate(attn_b, app_b, ms),
                     "frac": round(rate(attn_b, app_b, ms) / peak, 4),
                     "standalone": {"ms_per_launch": round(alone_ms, 4), "GB/s": round(alone, 1), "frac": round(alone / peak, 4)},
-                    "gpu_launches": launches, "kernel_status": job.kernel_status(), "kv_setup_seconds": round(job.setup_s, 1)}
+                    "gpu_launches": launches, "kernel_status": job.kernel_status(), "kv_setup_seconds": round(job.setup_s, 1),
+                    "clocks": {"sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}}
         finally:
             job.close()
     except Exception as exc:

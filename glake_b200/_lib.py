@@ -16,6 +16,7 @@ VT_ERR_UNSUPPORTED, VT_ERR_CUDA, VT_ERR_STATE, VT_ERR_NO_DRIVER, VT_ERR_KERNEL =
 VT_ERR_TOO_LARGE = 11
 VT_STATIC_SCRATCH_BYTES = 24 << 20
 VT_STEP_OVERLAP = 1
+VT_STEP_EARLY_KV = 2
 VT_KV_BF16, VT_KV_FP8_E4M3 = 0, 1
 
 

@@ -326,7 +326,7 @@ class DecodeRunner:
                             self.q[layer].view(b, self.impl.num_heads, self.impl.head_size), self.k[layer],
                             self.v[layer], kc.vmm_ptr, vc.vmm_ptr, self.d64[:b], self.d64[b:], self.d32[:b],
                             meta.max_seq_len, self.impl.num_kv_heads, self.impl.scale, self.impl.kv_cache_dtype,
-                            ks, vs, overlap=self.overlap and layer > 0, workspace=self.workspace)
+                            ks, vs, overlap=self._overlap_mode(layer), workspace=self.workspace)
             torch.cuda.nvtx.range_pop()
             if self.post_layer is not None:
                 self.post_layer(layer)
@@ -339,6 +339,15 @@ class DecodeRunner:
         if self.host_io:
             main.wait_stream(self.s_in)
             main.wait_stream(self.s_out)
+
+    def _overlap_mode(self, layer):
+        """Layer 0 follows the copies of the step's integers: an ordinary launch.  Later layers
+        overlap the previous layer's launch outright when nothing sits between them, and only
+        stream their old cache rows early when other kernels do (their q / k / v would be
+        those kernels' outputs in a model)."""
+        if not self.overlap or layer == 0:
+            return False
+        return "early_kv" if self.post_layer is not None else True
 
     def step(self, meta: VTensorMetadata):
         """Runs one decode step for ``meta`` (slot ids and context lengths as lists).
@@ -361,7 +370,9 @@ class DecodeRunner:
             self.d64.copy_(self.h64[cur], non_blocking=True)
             self.d32.copy_(self.h32[cur], non_blocking=True)
             if self.staged[cur] is None:
-                self.staged[cur] = torch.cuda.Event()
+                # blocking: a host thread that spins inside the driver while it waits slows the
+                # allocator's worker thread, whose cuMemMap / cuMemSetAccess calls need the same locks
+                self.staged[cur] = torch.cuda.Event(blocking=True)
             self.staged[cur].record(self.stream)
         bucket = (meta.max_seq_len + self.BUCKET - 1) // self.BUCKET * self.BUCKET
         graph = self.graphs.get(bucket)

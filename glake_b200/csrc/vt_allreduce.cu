@@ -413,6 +413,7 @@ __global__ void __launch_bounds__(kArThreads, 2) all_reduce_kernel(const __grid_
   const ArDev &d = L.dev[blockIdx.y];
   const uint4 *in = static_cast<const uint4 *>(L.in[blockIdx.y]);
   uint4 *out = static_cast<uint4 *>(L.out[blockIdx.y]);
+  pdl_launch_dependents();   // a programmatic dependent behind this call may start its own prologue now
   if (threadIdx.x == 0) timed_out = 0;
   __syncthreads();
   const bool push = n_vec <= d.push_vecs, push2 = !push && n_vec <= d.push2_vecs && d.world > 1;

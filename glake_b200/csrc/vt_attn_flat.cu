@@ -227,6 +227,7 @@ attn_flat_kernel(AttnParams p) {
           if (fresh && t0 + grp * R + rows == seq_len) {
             // the newest token comes straight from this step's input row
             --rows;
+            if (p.overlap == 2) pdl_wait_prior_grid();   // ... which the preceding kernel may still be writing
             if (!kFp8) bulk_g2s(dst + rows * HS * kRowB, fresh, HS * kRowB, full0 + 8 * s);
           }
           if (rows > 0)
@@ -281,6 +282,7 @@ attn_flat_kernel(AttnParams p) {
     }
     const float sl2 = kFp8 ? sl2_base * p.k_scale[kv_head] : sl2_base;   // fp8: K's scale folded into the logits
     W<NB> st;
+    if (p.overlap == 2) pdl_wait_prior_grid();   // q (and the new rows) may be the preceding kernel's output
     st.start(static_cast<const __nv_bfloat16 *>(p.q) + pc.b * p.q_stride + kv_head * g * kHeadDim, g, lane);
     for (int tile = pc.tile_begin; tile < pc.tile_end; ++tile, ++it) {
       const int s = it % kStages;

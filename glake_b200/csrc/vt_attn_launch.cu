@@ -233,7 +233,7 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
     vt::carve_flat(workspace, batch, kvh, &p);
     // Overlap only for the fused launch: a separate append kernel in front of this one
     // writes the row this launch reads, and only ordinary stream order covers that.
-    p.overlap = (fused && (flags & VT_STEP_OVERLAP)) ? 1 : 0;
+    p.overlap = !fused ? 0 : (flags & VT_STEP_EARLY_KV) ? 2 : (flags & VT_STEP_OVERLAP) ? 1 : 0;
     // The ticket counters return to zero at the end of every launch.  They are
     // cleared here anyway so that a scratch buffer of unknown content works — except
     // in overlap mode, where a memset between the kernels would serialise them and
@@ -339,7 +339,7 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
                    const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len, float scale,
                    int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
                    size_t workspace_bytes, unsigned flags, void *stream) {
-  if (batch < 0 || kvh <= 0 || (flags & ~static_cast<unsigned>(VT_STEP_OVERLAP))) return VT_ERR_INVALID;
+  if (batch < 0 || kvh <= 0 || (flags & ~static_cast<unsigned>(VT_STEP_OVERLAP | VT_STEP_EARLY_KV))) return VT_ERR_INVALID;
   if (batch == 0) return VT_OK;
   if (!key || !value || !byte_off) return VT_ERR_INVALID;
   if ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 15) return VT_ERR_INVALID;

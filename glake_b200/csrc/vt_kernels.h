@@ -73,7 +73,8 @@ struct AttnParams {
   const void *new_key, *new_value;    // bf16 [batch, kvh, 128]; nullptr = plain attention
   int64_t new_key_stride, new_value_stride;   // elements per batch row
   const int64_t *byte_off;            // destination byte offset per entry (negative = nothing to append)
-  int overlap;                        // launched as a programmatic dependent of the previous kernel on the stream
+  int overlap;                        // launched as a programmatic dependent of the previous kernel on the stream:
+                                      // 1 = its inputs are ready already, 2 = wait for that kernel before reading q / new rows
 };
 
 constexpr int kFlatMaxBatch = 1024;   // prefix table of the flat schedule lives in shared memory

@@ -238,7 +238,9 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
     appended token.  query/out ``[B, H, D]``, key/value ``[B, KVH, D]`` bf16.
     ``overlap=True`` lets the launch overlap the previous ``decode_step`` on the
     stream (VT_STEP_OVERLAP): only for a different layer's ranges, see vtensor.h;
-    pass a private zero-filled ``workspace`` (uint8 tensor) in that case."""
+    ``overlap="early_kv"`` (VT_STEP_EARLY_KV) is the form for inputs that the preceding
+    kernel produces: cache rows stream early, q / key / value are read after it finished.
+    Pass a private zero-filled ``workspace`` (uint8 tensor) in both cases."""
     _require_cuda(out, query, key, value, slot_m, slot_mapping, seq_lens)
     batch, num_heads, head_size = query.shape
     key = key.view(batch, num_kv_heads, head_size)
@@ -253,7 +255,7 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
                                  c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens), batch, num_heads,
                                  num_kv_heads, head_size, int(max_seq_len), float(scale), _kv_dtype(kv_cache_dtype),
                                  _ptr(k_scale), _ptr(v_scale), _ptr(lse), _ptr(ws), ws.numel(),
-                                 1 if overlap else 0, _stream()),
+                                 2 if overlap == "early_kv" else (1 if overlap else 0), _stream()),
               "vt_decode_step")
 
 

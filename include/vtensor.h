@@ -272,8 +272,18 @@ int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype
  * — q, key, value, seq_lens, slot_ids, byte_off, the slots' ranges — is written by
  * the previous kernel on the stream (consecutive LAYERS of one step qualify; two
  * steps on the same layer do not), and (2) the workspace was zero-filled once
- * after allocation and is used by nothing but these calls. */
+ * after allocation and is used by nothing but these calls.
+ * VT_STEP_EARLY_KV is the form for a step whose q / key / value ARE produced by the
+ * kernel in front of it (the usual case inside a model): the launch is again a
+ * programmatic dependent, reads its metadata (seq_lens, slot_ids, byte_off, the
+ * tables — none of them written by that kernel) and starts streaming the cache
+ * rows of earlier tokens at once, but waits for the preceding kernel to complete
+ * before it touches q, key, value or the scratch.  It hides the launch ramp and the
+ * fill of the copy ring behind the tail of the preceding kernel when that kernel
+ * releases its dependents early (vt_all_reduce and vt_decode_step do); behind any
+ * other kernel it behaves like an ordinary launch.  Condition (2) applies. */
 #define VT_STEP_OVERLAP 1u
+#define VT_STEP_EARLY_KV 2u
 int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *key,
                    const void *value, int64_t key_stride, int64_t value_stride, const int64_t *byte_off,
                    const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,

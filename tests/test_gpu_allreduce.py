@@ -134,13 +134,14 @@ def test_emulated_two_phase_push_path(oracle, world, n_ctas):
                  (1 << 17) + 8, 1 << 19, 1 << 19, 1 << 19]
         for call, n in enumerate(sizes):
             ins = _inputs(9000 + 10 * world + call, world, n)
-            for t in ins:
-                t[8:10] = -0.0                                        # every rank sends the sentinel pattern there
-                t[12] = -0.0
-            ins[0][16:18] = 1.5                                       # ... and here values cancel to zero next to negative zeros
-            ins[1][16:18] = -1.5
-            for t in ins[2:]:
-                t[16:18] = -0.0
+            if n >= 24:
+                for t in ins:
+                    t[8:10] = -0.0                                    # every rank sends the sentinel pattern there
+                    t[12] = -0.0
+                ins[0][16:18] = 1.5                                   # ... and here values cancel to zero next to negative zeros
+                ins[1][16:18] = -1.5
+                for t in ins[2:]:
+                    t[16:18] = -0.0
             want = oracle.port_all_reduce(ins)
             d_in = [t.cuda() for t in ins]
             d_out = [torch.empty_like(t) for t in d_in] if call % 3 else d_in

@@ -243,3 +243,85 @@ def test_backend_prompt_extend_decode_over_an_fp8_cache(G, oracle, h, kvh):
                 assert bool((err <= tol).all()), (phase, layer, float((err - tol).max()))
     finally:
         eng.close()
+
+
+@pytest.mark.parametrize("h,kvh,fp8", [(8, 1, False), (8, 8, False), (8, 8, True)])
+def test_early_kv_launch_reads_inputs_the_preceding_kernel_produces(G, oracle, h, kvh, fp8):
+    """With other kernels between the layers' attention launches the runner uses the
+    early-KV form of the step: launched as a programmatic dependent, it may stream old
+    cache rows while the kernel in front of it still runs, but must not read q / k / v
+    before that kernel finished.  Here that kernel is a one-rank vt_all_reduce (a copy
+    that releases its dependents at once) which WRITES the next layer's q, k and v over
+    NaN-filled buffers."""
+    import ctypes
+    from glake_b200 import ops
+    from glake_b200.backend import DecodeRunner, VTensorAttentionImpl, VTensorCacheEngine, VTensorMetadata, prepare_step
+    from tests.test_gpu_allreduce import Emulated
+    layers, lens0 = 3, [300, 2, 1500, 65, 700, 129]
+    b = len(lens0)
+    dt = "fp8_e4m3" if fp8 else "auto"
+    rs = np.random.RandomState(777 + kvh)
+    eng = VTensorCacheEngine(layers, kvh, 128, b, 2048, cache_dtype=dt)
+    impl = VTensorAttentionImpl(h, 128, SCALE, kvh, kv_cache_dtype=dt)
+    E = Emulated(1, max_bytes=1 << 20)
+    try:
+        pre = [n - 1 for n in lens0]
+        hist_k = [[synth.normal_bf16(rs, n, kvh, 128) for n in pre] for _ in range(layers)]
+        hist_v = [[synth.normal_bf16(rs, n, kvh, 128) for n in pre] for _ in range(layers)]
+        ks = vs = None
+        if fp8:
+            ks = torch.stack([ops.kv_scales(torch.cat(hist_k[l]).cuda(), kvh, 128) for l in range(layers)])
+            vs = torch.stack([ops.kv_scales(torch.cat(hist_v[l]).cuda(), kvh, 128) for l in range(layers)])
+        slots = list(range(b))
+        meta = VTensorMetadata(slots, pre, kvh, 128, num_prefills=b, kv_elem_size=1 if fp8 else 2)
+        prepare_step(meta, eng)
+        for l in range(layers):
+            ops.reshape_and_cache(torch.cat(hist_k[l]).cuda(), torch.cat(hist_v[l]).cuda(), eng.k_cache_ptr[l],
+                                  eng.v_cache_ptr[l], meta.slot_m, meta.slot_mapping, meta.seq_lens_tensor,
+                                  meta.cache_seq_lens, max(pre), kvh, 128, dt, ks[l] if fp8 else None,
+                                  vs[l] if fp8 else None)
+        src = {}
+
+        def produce_next_inputs(layer):
+            nxt = layer + 1
+            if nxt >= layers:
+                return
+            stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            for name in ("q", "k", "v"):
+                dst = getattr(runner, name)[nxt]
+                E.check(E.lib.vt_all_reduce(E.ars[0], ctypes.c_void_p(src[name][nxt].data_ptr()),
+                                            ctypes.c_void_p(dst.data_ptr()), dst.numel(), stream), "vt_all_reduce")
+
+        runner = DecodeRunner(eng, impl, b, host_io=False, k_scale=ks, v_scale=vs, overlap=True,
+                              post_layer=produce_next_inputs, launches_per_post_layer=3)
+        assert runner._overlap_mode(1) == "early_kv"
+        for name in ("q", "k", "v"):
+            src[name] = torch.zeros_like(getattr(runner, name))
+        lens = list(pre)
+        for step in range(3):
+            lens = [n + 1 for n in lens]
+            q = synth.normal_bf16(rs, layers, b, h * 128)
+            nk = synth.normal_bf16(rs, layers, b, kvh * 128)
+            nv = synth.normal_bf16(rs, layers, b, kvh * 128)
+            src["q"].copy_(q), src["k"].copy_(nk), src["v"].copy_(nv)
+            for name, t in (("q", q), ("k", nk), ("v", nv)):       # layer 0 gets its inputs directly, the others NaN
+                getattr(runner, name).fill_(float("nan"))
+                getattr(runner, name)[0].copy_(t[0])
+            torch.cuda.synchronize()
+            runner.step(VTensorMetadata(slots, lens, kvh, 128, num_decode_tokens=b, kv_elem_size=1 if fp8 else 2))
+            runner.synchronize()
+            for l in range(layers):
+                hist_k[l] = [torch.cat([a, x.view(1, kvh, 128)]) for a, x in zip(hist_k[l], nk[l])]
+                hist_v[l] = [torch.cat([a, x.view(1, kvh, 128)]) for a, x in zip(hist_v[l], nv[l])]
+                sk, sv = (ks[l].cpu(), vs[l].cpu()) if fp8 else (None, None)
+                r = oracle.fill_ranges(hist_k[l], hist_v[l], k_scale=sk, v_scale=sv)
+                port = oracle.port_decode_attn(q[l].view(b, h, 128), r, torch.arange(b), torch.tensor(lens, dtype=torch.int32),
+                                               kvh, SCALE, sk, sv)
+                got = runner.out[l].view(b, h, 128).cpu()
+                err = (got.float() - port.float()).abs()
+                tol = torch.maximum(torch.full_like(err, 1e-2 if fp8 else 2e-3), port.float().abs() * 2.0 ** (-6 if fp8 else -7))
+                assert bool((err <= tol).all()), (step, l, float(err.nan_to_num(nan=9e9).max()))
+        assert runner.status() == 0 and E.status(0) == 0
+    finally:
+        E.close()
+        eng.close()
