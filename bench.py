@@ -416,27 +416,70 @@ def load_peaks():
         return {}
 
 
-def op_record(name, seed, steps, peak, with_cpu=False):
-    """Extra record for one of the op-level configurations: >= 100 graph-replayed calls
-    (append one token + attend), CUDA events, no overlap between consecutive calls."""
+def op_record(name, seed, calls, peak, with_cpu=False):
+    """Extra record for one of the op-level configurations: the fused call (append one token,
+    then attend) replayed >= `calls` times from CUDA graphs of 20 back-to-back calls, CUDA
+    events around the replays, no overlap between consecutive calls.  Every call appends the
+    same row at the same position (idempotent), so the contexts stay as generated."""
     try:
-        job = Job(name, seed, 0, 1, steps + 8)
+        import torch
+        from glake_b200 import ops
+        from glake_b200.backend import prepare_step
+        job = Job(name, seed, 0, 1, 8)
         try:
-            r = job.runner("op", overlap=False)
-            sampler = ClockSampler(job.dev.index)
-            ms, attn_b, app_b, launches, _ = timed(job, r, steps, 3, 1, sampler)
-            clocks = sampler.stop()
-            calls = steps * job.layers
-            from glake_b200 import ops
-            _, parts, variant = ops.attn_plan(job.b, job.h, job.kvh, max(job.lens), job.dtype)
+            meta = prepare_step(job._meta(), job.engine)
+            b, h, kvh = job.b, job.h, job.kvh
+            g = torch.Generator(device=job.dev).manual_seed(4321)
+            q = torch.randn(job.layers, b, h, D, device=job.dev, dtype=torch.bfloat16, generator=g)
+            k = torch.randn(job.layers, b, kvh, D, device=job.dev, dtype=torch.bfloat16, generator=g)
+            v = torch.randn(job.layers, b, kvh, D, device=job.dev, dtype=torch.bfloat16, generator=g)
+            out = torch.empty_like(q)
+            ws = ops.new_workspace(job.dev, b, h, D, meta.max_seq_len)
+
+            def one_pass():
+                for layer in range(job.layers):
+                    kc, vc = job.engine.gpu_cache[layer]
+                    ops.decode_step(out[layer], q[layer], k[layer], v[layer], kc.vmm_ptr, vc.vmm_ptr, meta.slot_m,
+                                    meta.slot_mapping, meta.seq_lens_tensor, meta.max_seq_len, kvh, D ** -0.5, job.dtype,
+                                    job.scale_k[layer] if job.fp8 else None, job.scale_v[layer] if job.fp8 else None,
+                                    workspace=ws)
+            per_graph = max(1, 20 // job.layers) * job.layers
+            side = torch.cuda.Stream(device=job.dev)
+            with torch.cuda.stream(side):
+                one_pass()
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(per_graph // job.layers):
+                        one_pass()
+                for _ in range(3):
+                    graph.replay()
+                side.synchronize()
+                replays = -(-calls // per_graph)
+                sampler = ClockSampler(job.dev.index)
+                sampler.mark_begin()
+                a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(side)
+                for _ in range(replays):
+                    graph.replay()
+                z.record(side)
+                side.synchronize()
+                sampler.mark_end()
+                clocks = sampler.stop()
+            n_calls = replays * per_graph
+            ms = a.elapsed_time(z) / n_calls
+            status = ops.workspace_status(ws)
+            del graph
+            attn_b, _ = algorithmic_bytes(job.lens, 1, h, kvh, job.e)
+            _, parts, variant = ops.attn_plan(b, h, kvh, max(job.lens), job.dtype)
             gbs = attn_b / (ms * 1e-3) / 1e9
-            rec = {"workload": WORKLOAD_TEXT[name], "calls": calls, "ms_per_call": round(ms / calls, 5),
-                   "algorithmic_bytes_per_call": int(attn_b / calls), "GB/s": round(gbs, 1),
+            rec = {"workload": WORKLOAD_TEXT[name], "calls": n_calls, "ms_per_call": round(ms, 5),
+                   "algorithmic_bytes_per_call": int(attn_b), "GB/s": round(gbs, 1),
                    "frac": round(gbs / peak, 4), "pct_of_nominal_8TBs": round(gbs / 80.0, 1),
                    "kernel": ["simt split-k", "tensor-core split-k", "tensor-core flat persistent"][variant]
-                             + (", fused append" if ops.step_is_fused(job.dtype) else ", separate append kernel"),
-                   "gpu_launches": launches, "kernel_status": job.kernel_status(),
-                   "how": "CUDA graph replays back to back, CUDA events, contexts grow by one token per call",
+                             + (", fused append" if variant == 2 and ops.step_is_fused(job.dtype) else ", separate append kernel"),
+                   "gpu_launches": n_calls, "kernel_status": status,
+                   "how": f"CUDA graphs of {per_graph} calls back to back, CUDA events around {replays} replays",
                    "clocks": {"sm_mhz": clocks.get("sm_mhz"), "reasons": clocks.get("reasons")}}
             if job.layers > 1:
                 rec["l2"] = f"{job.layers} independent copies of the ranges cycled, so no call finds its KV in L2"
