@@ -1093,6 +1093,10 @@ def op_allreduce(sizes):
 
 if __name__ == "__main__":
     a = parse()
+    if a.impl == "reference":
+        # torchrun exports OMP_NUM_THREADS=1 for its children; the reference's CPU kernels are OpenMP code
+        # and this arm is meant to use every host core.  Must happen before any OpenMP runtime loads.
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     if a.op:
         op_main(a.op)
     elif a.impl == "reference":
