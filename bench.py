@@ -187,6 +187,10 @@ class Collectives:
         self.x = [torch.zeros(batch, hidden, dtype=torch.bfloat16, device=device) for _ in range(2)]
         self.y = [torch.zeros_like(t) for t in self.x]
         self.comm = None
+        self.buffers = "plain device tensors"
+        self._pool = self._backend = None
+        if kind == "nccl":
+            self._try_registered_buffers(batch, hidden, device)
         if kind == "peer":
             from glake_b200 import tp
             self.comm = tp.PeerAllReduce(max_size=max(1 << 20, batch * hidden * 2))
@@ -200,6 +204,76 @@ class Collectives:
         for t in self.x + self.y:
             t.zero_()
         torch.cuda.synchronize()
+
+    def _graph_time(self, tensors, calls=20, replays=3):
+        """Device time (ms, max over ranks) of `calls` NCCL all-reduces replayed from a CUDA graph."""
+        import torch
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.dist.all_reduce(tensors[0])
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side, capture_error_mode="thread_local"):
+                for i in range(calls):
+                    self.dist.all_reduce(tensors[i % 2])
+            best = float("inf")
+            for _ in range(replays):
+                self.dist.barrier()
+                torch.cuda.synchronize()
+                a, z = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(side)
+                g.replay()
+                z.record(side)
+                side.synchronize()
+                best = min(best, a.elapsed_time(z))
+            del g
+        torch.cuda.synchronize()
+        t = torch.tensor([best], dtype=torch.float64, device="cuda")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def _try_registered_buffers(self, batch, hidden, device):
+        """NCCL can run its all-reduce on buffers that come from its own allocator and are
+        registered with the communicator as a symmetric window (torch: a MemPool over the
+        backend's allocator + register_mem_pool(pool, symm=True)).  On 8 B200s that takes the
+        1 MiB call from 41 to 29 us; on 2 it is slower.  Both kinds of buffer are timed here
+        (20 graph-replayed calls, max over ranks) and the faster one is used; any failure of
+        the registration path leaves the plain tensors in place.  Collective: every rank
+        takes the same decisions because they rest on all-reduced numbers."""
+        import torch
+        ok = torch.ones(1, device=device)
+        try:
+            pg = self.dist.distributed_c10d._get_default_group()
+            backend = pg._get_backend(torch.device("cuda", torch.cuda.current_device()))
+            pool = torch.cuda.MemPool(backend.mem_allocator)
+            with torch.cuda.use_mem_pool(pool):
+                reg = [torch.zeros(batch, hidden, dtype=torch.bfloat16, device=device) for _ in range(2)]
+            backend.register_mem_pool(pool, True)
+        except Exception:
+            ok.zero_()
+            reg = pool = backend = None
+        self.dist.all_reduce(ok, op=self.dist.ReduceOp.MIN)
+        if float(ok.item()) == 0.0:
+            if pool is not None:
+                try:
+                    backend.deregister_mem_pool(pool)
+                except Exception:
+                    pass
+            return
+        t_plain, t_reg = self._graph_time(self.x), self._graph_time(reg)
+        if t_reg < t_plain:
+            self.x, self._pool, self._backend = reg, pool, backend
+            self.buffers = (f"NCCL-allocated, registered as a symmetric window "
+                            f"({t_reg / 20 * 1e3:.1f} us per call vs {t_plain / 20 * 1e3:.1f} us on plain tensors)")
+        else:
+            self.buffers = (f"plain device tensors ({t_plain / 20 * 1e3:.1f} us per call vs "
+                            f"{t_reg / 20 * 1e3:.1f} us on NCCL-registered symmetric buffers)")
+            del reg
+            try:
+                backend.deregister_mem_pool(pool)
+            except Exception:
+                pass
 
     def __call__(self, layer):
         if self.kind == "peer":
@@ -216,6 +290,15 @@ class Collectives:
         if self.comm is not None:
             self.comm.close()
             self.comm = None
+        if self._pool is not None:
+            import torch
+            torch.cuda.synchronize()
+            self.x = []
+            try:
+                self._backend.deregister_mem_pool(self._pool)
+            except Exception:
+                pass
+            self._pool = self._backend = None
 
 
 class Job:
@@ -628,6 +711,8 @@ def run_ours(args):
         if peer is not None:
             peer.close()
         job.close()
+        if nccl is not None:
+            nccl.close()
         dist.barrier()
         dist.destroy_process_group()
         return
@@ -663,7 +748,8 @@ def run_ours(args):
                                 "variant": ["simt split-k", "tensor-core split-k", "tensor-core flat persistent"][variant]},
                     "kv_setup_seconds": round(job.setup_s, 1), "cuda_graph": True,
                     "collectives_in_step": "2 x NCCL all-reduce of [batch, hidden] bf16 per layer, inside the CUDA graph"
-                    if world > 1 else "none (one GPU)"},
+                    if world > 1 else "none (one GPU)",
+                    "nccl_buffers": nccl.buffers if nccl is not None else None},
         "path_tokens_per_s": round(b * K / (ms * 1e-3), 1),
         "path_tokens_per_s_note": "decode steps of the hot path only: no weight GEMMs are executed",
         "step_ms": {"min": round(step_ms[0], 3), "median": round(step_ms[len(step_ms) // 2], 3), "max": round(step_ms[-1], 3)},
@@ -691,6 +777,8 @@ def run_ours(args):
     if peer is not None:
         peer.close()
     job.close()
+    if nccl is not None:
+        nccl.close()
     if world == 1 and extras and name == "7b":
         line["configs"] = {"op1": op_record("op1", args.seed, 100, peak, with_cpu=not args.no_cpu_baseline),
                            "gqa-long": op_record("gqa-long", args.seed, 100, peak),
