@@ -79,13 +79,23 @@ int sm_count() {
   return v;
 }
 
+// The tile list is cut evenly in COST units, not in tiles: every stream is preceded by
+// kBoundaryCost phantom positions that carry no data.  A CTA whose share crosses from one
+// stream into the next stops computing for a while (publish the piece, fence, ticket,
+// possibly merge, load the next Q): measured 4.4 us against 1.4 us per 32 KB tile, and the
+// CTAs with such a crossing were the last to finish by that margin.  With the phantom
+// positions inside its share, a crossing CTA gets that many fewer real tiles.
+constexpr int kBoundaryCost = 3;
+
 struct Piece {
-  int b, slab, tile_begin, tile_end, tiles_in_stream;
-  long long stream_begin;  // global index of the stream's first tile
+  int b, slab, tile_begin, tile_end, tiles_in_stream;   // real tiles [tile_begin, tile_end) of the stream (may be empty)
+  long long stream_begin;  // position of the stream's first phantom position
+  long long stream_end;    // position after the stream's last tile
+  int advance;             // positions of the share this piece uses up
 };
 
-// Locates the stream holding global tile `tau` and the run of tiles this CTA
-// owns inside it.  prefix[b] = global index of sequence b's first tile.
+// Locates the stream holding position `tau` and the run of tiles this CTA owns inside
+// it.  prefix[b] = position of sequence b's first stream.
 __device__ __forceinline__ Piece locate(const int *prefix, int batch, int slabs, long long tau, long long tau_end) {
   int lo = 0, hi = batch;  // largest b with prefix[b] <= tau
   while (hi - lo > 1) {
@@ -94,14 +104,17 @@ __device__ __forceinline__ Piece locate(const int *prefix, int batch, int slabs,
   }
   Piece pc;
   pc.b = lo;
-  const int per_slab = (prefix[lo + 1] - prefix[lo]) / slabs;
+  const int per_slab = (prefix[lo + 1] - prefix[lo]) / slabs;      // phantom positions + tiles
   const int rem = static_cast<int>(tau - prefix[lo]);
   pc.slab = rem / per_slab;
-  pc.tile_begin = rem % per_slab;
-  pc.tiles_in_stream = per_slab;
+  const int pos = rem % per_slab;
+  pc.tiles_in_stream = per_slab - kBoundaryCost;
   pc.stream_begin = prefix[lo] + static_cast<long long>(pc.slab) * per_slab;
-  const long long room = tau_end - tau;
-  pc.tile_end = static_cast<int>(min(static_cast<long long>(per_slab), pc.tile_begin + room));
+  pc.stream_end = pc.stream_begin + per_slab;
+  const int end = static_cast<int>(min(static_cast<long long>(per_slab), pos + (tau_end - tau)));
+  pc.advance = end - pos;
+  pc.tile_begin = max(pos - kBoundaryCost, 0);
+  pc.tile_end = max(end - kBoundaryCost, 0);
   return pc;
 }
 
@@ -151,7 +164,7 @@ attn_flat_kernel(AttnParams p) {
   for (int i = threadIdx.x; i < p.batch; i += kThreads) {
     const int len = max(p.seq_lens[i], 0);
     lens[i] = len;
-    prefix[i + 1] = ((len + TILE_TOK - 1) / TILE_TOK) * slabs;
+    prefix[i + 1] = len > 0 ? ((len + TILE_TOK - 1) / TILE_TOK + kBoundaryCost) * slabs : 0;
     if (cache_bases) {   // resolve slot -> range base once, off the producer's critical path
       const int64_t slot = p.slot_ids[i];
       kbase_s[i] = p.k_table[slot];
@@ -235,7 +248,7 @@ attn_flat_kernel(AttnParams p) {
                           full0 + 8 * s, policy);
         }
       }
-      tau += pc.tile_end - pc.tile_begin;
+      tau += pc.advance;
     }
     return;
   }
@@ -265,6 +278,10 @@ attn_flat_kernel(AttnParams p) {
   bool first_piece = true;
   for (long long tau = tau0; tau < tau1;) {
     const Piece pc = locate(prefix, p.batch, slabs, tau, tau1);
+    if (pc.tile_end <= pc.tile_begin) {   // only phantom positions of this stream fall into the share
+      tau += pc.advance;
+      continue;
+    }
     const int seq_len = lens[pc.b];
     const int kv_head = pc.slab * HS + hs;
     long long append_off = -1;
@@ -359,7 +376,8 @@ attn_flat_kernel(AttnParams p) {
       if (p.overlap) pdl_wait_prior_grid();
       const int slot_id = first_piece ? 0 : 1;
       float *slot_base = p.fl_part + (static_cast<size_t>(blockIdx.x) * 2 + slot_id) * kCWarps * HEADS * kPartRow;
-      const bool last_of_cta = tau + (pc.tile_end - pc.tile_begin) == tau1;
+      // the CTA's last piece: whatever is left of the share after this stream is phantom
+      const bool last_of_cta = tau1 <= pc.stream_end + kBoundaryCost;
       if (R > 1 && last_of_cta) {
         // The ring is idle after the CTA's last tile: fold the R warps of every kv
         // head together in shared memory first, so the piece publishes one state
@@ -391,8 +409,9 @@ attn_flat_kernel(AttnParams p) {
       }
       __threadfence();
       named_bar_sync(1, kCWarps * 32);
-      const long long s_begin = pc.stream_begin, s_end = pc.stream_begin + pc.tiles_in_stream;
-      const int c_first = owner_of(s_begin, total, n_ctas), c_last = owner_of(s_end - 1, total, n_ctas);
+      // pieces of the stream = CTAs whose shares hold real tiles of it
+      const long long s_begin = pc.stream_begin, s_end = pc.stream_end;
+      const int c_first = owner_of(s_begin + kBoundaryCost, total, n_ctas), c_last = owner_of(s_end - 1, total, n_ctas);
       const int n_pieces = c_last - c_first + 1;
       if (tid == 0) {
         unsigned *ctr = p.fl_count + pc.b * slabs + pc.slab;
@@ -413,7 +432,7 @@ attn_flat_kernel(AttnParams p) {
         // 16-byte loads.  Streams cut into more than 32 sources go in rounds.
         // Pieces that were their CTA's last piece arrive folded (one row per head):
         // that is every piece but, possibly, the one in the stream's last CTA.
-        const bool last_folded = R == 1 || s_end >= total * (c_last + 1) / n_ctas;
+        const bool last_folded = R == 1 || total * (c_last + 1) / n_ctas <= s_end + kBoundaryCost;
         const int n_single = last_folded ? n_pieces : n_pieces - 1;
         const int n_src = R == 1 ? n_pieces : n_single + (last_folded ? 0 : R);
         for (int item = warp; item < HS * g; item += kCWarps) {
@@ -433,6 +452,24 @@ attn_flat_kernel(AttnParams p) {
               mi = __ldcg(mine + 128);
               li = __ldcg(mine + 129);
             }
+            // Eight independent 16-byte loads in flight per lane; absent sources carry
+            // weight 0 and re-read the lane's own row (or source 0's), never garbage.  The
+            // first eight go out together with the (max, sum) loads above: their addresses
+            // need no data, only the weights do, so a stream cut into up to eight sources
+            // is merged in ONE round trip to L2.
+            const unsigned long long mine_bits = reinterpret_cast<unsigned long long>(mine);
+            const unsigned long long any_bits = __shfl_sync(0xffffffffu, mine_bits, 0);
+            const int cnt = min(32, n_src - s0);
+            auto fetch = [&](int j0, float4 (&v)[8]) {
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                unsigned long long bits = __shfl_sync(0xffffffffu, mine_bits, min(j0 + u, 31));
+                if (bits == 0ull) bits = any_bits;
+                v[u] = __ldcg(reinterpret_cast<const float4 *>(bits) + lane);
+              }
+            };
+            float4 v[8];
+            fetch(0, v);
             float mx = mi;
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
@@ -445,25 +482,11 @@ attn_flat_kernel(AttnParams p) {
             L = L * rescale + ls;
             acc.x *= rescale; acc.y *= rescale; acc.z *= rescale; acc.w *= rescale;
             M = Mn;
-            // Eight independent 16-byte loads in flight per lane; absent sources carry
-            // weight 0 and re-read the lane's own row (or source 0's), never garbage.
-            const unsigned long long mine_bits = reinterpret_cast<unsigned long long>(mine);
-            const unsigned long long any_bits = __shfl_sync(0xffffffffu, mine_bits, 0);
-            const int cnt = min(32, n_src - s0);
             for (int j0 = 0; j0 < cnt; j0 += 8) {
-              float f[8];
-              float4 v[8];
+              if (j0 > 0) fetch(j0, v);
 #pragma unroll
               for (int u = 0; u < 8; ++u) {
-                const int j = min(j0 + u, 31);
-                f[u] = __shfl_sync(0xffffffffu, fi, j);
-                unsigned long long bits = __shfl_sync(0xffffffffu, mine_bits, j);
-                if (bits == 0ull) bits = any_bits;
-                v[u] = __ldcg(reinterpret_cast<const float4 *>(bits) + lane);
-              }
-#pragma unroll
-              for (int u = 0; u < 8; ++u) {
-                const float w = j0 + u < cnt ? f[u] : 0.f;
+                const float w = j0 + u < cnt ? __shfl_sync(0xffffffffu, fi, min(j0 + u, 31)) : 0.f;
                 acc.x = fmaf(w, v[u].x, acc.x); acc.y = fmaf(w, v[u].y, acc.y);
                 acc.z = fmaf(w, v[u].z, acc.z); acc.w = fmaf(w, v[u].w, acc.w);
               }
@@ -485,7 +508,7 @@ attn_flat_kernel(AttnParams p) {
       }
     }
     first_piece = false;
-    tau += pc.tile_end - pc.tile_begin;
+    tau += pc.advance;
   }
   if (failed && lane == 0) atomicExch(p.status, kKernelErrMagic);
 }
