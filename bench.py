@@ -525,7 +525,7 @@ def op_record(name, seed, calls, peak, with_cpu=False):
                     ops.decode_step(out[layer], q[layer], k[layer], v[layer], kc.vmm_ptr, vc.vmm_ptr, meta.slot_m,
                                     meta.slot_mapping, meta.seq_lens_tensor, meta.max_seq_len, kvh, D ** -0.5, job.dtype,
                                     job.scale_k[layer] if job.fp8 else None, job.scale_v[layer] if job.fp8 else None,
-                                    workspace=ws)
+                                    workspace=ws, maps=job.engine.decode_maps(layer, h))
             per_graph = max(1, 20 // job.layers) * job.layers
             side = torch.cuda.Stream(device=job.dev)
             with torch.cuda.stream(side):
@@ -988,7 +988,7 @@ def _time_calls(run, iters, flush=True):
 
 
 def op_main(argv):
-    """--op decode B H KVH LO HI [fp8 0|1] [num_splits] [iters]    one layer's decode attention call
+    """--op decode B H KVH LO HI [fp8 0|1] [num_splits] [iters] [tcgen05 0|1]    one layer's decode attention call
        --op prefill B H KVH L [tma 0|1] [iters]                    causal prefill over the ranges, TFLOP/s
        --op rope TOKENS H KVH [fp8 0|1] [iters]                    RoPE fused with the KV append
        --op norm TOKENS HIDDEN [iters]                             rms_norm / fused_add_rms_norm
@@ -1009,6 +1009,7 @@ def op_main(argv):
         fp8 = len(ints) > 5 and ints[5] == 1
         splits = ints[6] if len(ints) > 6 else 0
         iters = ints[7] if len(ints) > 7 else 20
+        tma = len(ints) > 8 and ints[8] == 1      # fp8 only: the tcgen05 kernel over tensor maps
         e = 1 if fp8 else 2
         lens = context_lens(0, B, LO, HI)
         row = KVH * D * e
@@ -1028,13 +1029,14 @@ def op_main(argv):
         q = torch.randn(B, H, D, device="cuda", dtype=torch.bfloat16)
         out = torch.empty_like(q)
         kc, vc = eng.gpu_cache[0]
+        maps = eng.decode_maps(0, H) if tma else None
 
         def run():
             ops.paged_attention_v1(out, q, kc.vmm_ptr, vc.vmm_ptr, KVH, D ** -0.5, meta.seq_lens_tensor, 1, max(lens), None,
-                                   dt, 1.0, meta.slot_mapping, k_scale=ks, v_scale=vs, num_splits=splits)
+                                   dt, 1.0, meta.slot_mapping, k_scale=ks, v_scale=vs, num_splits=splits, maps=maps)
         ms, best = _time_calls(run, iters)
         byt = tot * 2 * KVH * D * e + 2 * B * H * D * 2
-        print(f"decode B{B} H{H} KVH{KVH} L[{LO},{HI}] fp8={fp8} splits={splits} plan={ops.attn_plan(B, H, KVH, max(lens), dt, splits)}: "
+        print(f"decode B{B} H{H} KVH{KVH} L[{LO},{HI}] fp8={fp8} splits={splits} tcgen05={maps is not None} plan={ops.attn_plan(B, H, KVH, max(lens), dt, splits)}: "
               f"{ms * 1e3:.1f} us  {byt / ms / 1e6:.0f} GB/s  ({byt / 2 ** 20:.0f} MiB)  best {byt / best / 1e6:.0f} GB/s  "
               f"status {ops.attn_status()}", flush=True)
     elif mode == "prefill":

@@ -99,6 +99,9 @@ def _load():
                                    c_float, c_int, vp, vp, vp, vp, sz, c_int, vp]),
         "vt_decode_step": (c_int, [vp, c_int64, vp, c_int64, vp, vp, c_int64, c_int64, vp, vp, vp, vp, vp, c_int, c_int,
                                    c_int, c_int, c_int, c_float, c_int, vp, vp, vp, vp, sz, ctypes.c_uint, vp]),
+        "vt_decode_step_tma": (c_int, [vp, c_int64, vp, c_int64, vp, vp, c_int64, c_int64, vp, vp, vp, vp, vp, c_int, c_int,
+                                       c_int, c_int, c_int, c_float, c_int, vp, vp, vp, vp, sz, ctypes.c_uint, vp, vp]),
+        "vt_decode_maps_encode": (c_int, [vp, vp, c_int, c_int, c_int, c_int, c_uint64, vp]),
         "vt_prefill_attn": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,
                                     c_float, c_int, vp, vp]),
         "vt_prefill_attn_tma": (c_int, [vp, c_int64, vp, c_int64, vp, vp, vp, vp, vp, vp, c_int, c_int, c_int, c_int, c_int,

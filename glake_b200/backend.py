@@ -94,8 +94,23 @@ class VTensorCacheEngine:
                 self.num_kv_heads, self.head_size, self.max_context_size // self.token_size, self.device)
         return self._prefill_maps[layer]
 
+    def decode_maps(self, layer, num_heads):
+        """TMA tensor maps of this layer's fp8 ranges for ``ops.decode_step(..., maps=...)`` (the
+        tcgen05 decode kernel; built on first use; None when the shape or cache dtype rules it out)."""
+        if self.dtype_size != 1 or not ops.decode_tma_supported(num_heads, self.num_kv_heads, "fp8_e4m3"):
+            return None
+        if not hasattr(self, "_decode_maps"):
+            self._decode_maps = {}
+        if layer not in self._decode_maps:
+            segs = self.vmm_kvcache_segment
+            self._decode_maps[layer] = ops.decode_maps(
+                [s.getKeyDevicePtr(layer) for s in segs], [s.getValueDevicePtr(layer) for s in segs],
+                self.num_kv_heads, self.head_size, self.max_context_size // self.token_size, self.device)
+        return self._decode_maps[layer]
+
     def close(self):
         self._prefill_maps = {}
+        self._decode_maps = {}
         for k, v in self.gpu_cache:
             k.kv_cache.close()
             v.kv_cache.close()
@@ -326,7 +341,8 @@ class DecodeRunner:
                             self.q[layer].view(b, self.impl.num_heads, self.impl.head_size), self.k[layer],
                             self.v[layer], kc.vmm_ptr, vc.vmm_ptr, self.d64[:b], self.d64[b:], self.d32[:b],
                             meta.max_seq_len, self.impl.num_kv_heads, self.impl.scale, self.impl.kv_cache_dtype,
-                            ks, vs, overlap=self._overlap_mode(layer), workspace=self.workspace)
+                            ks, vs, overlap=self._overlap_mode(layer), workspace=self.workspace,
+                            maps=self.engine.decode_maps(layer, self.impl.num_heads))
             torch.cuda.nvtx.range_pop()
             if self.post_layer is not None:
                 self.post_layer(layer)

@@ -197,7 +197,7 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
                    float scale, int kv_dtype, const float *k_scale, const float *v_scale,
                    float *lse, void *workspace, size_t workspace_bytes, int num_splits,
                    void *stream, const void *new_key, const void *new_value, int64_t new_key_stride,
-                   int64_t new_value_stride, const int64_t *byte_off, unsigned flags) {
+                   int64_t new_value_stride, const int64_t *byte_off, unsigned flags, const void *maps = nullptr) {
   if (batch < 0 || h <= 0 || kvh <= 0 || max_seq_len < 0 || num_splits < 0) return VT_ERR_INVALID;
   if (batch == 0) return VT_OK;
   if (!out || !q || !k_table || !v_table || !slot_ids || !seq_lens || !workspace) return VT_ERR_INVALID;
@@ -241,6 +241,11 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
     if (!p.overlap &&
         cudaMemsetAsync(p.fl_count, 0, static_cast<size_t>(batch) * kvh * sizeof(unsigned), s) != cudaSuccess)
       return VT_ERR_CUDA;
+    // fp8 ranges with tensor maps: the tcgen05 engine where the shape allows (same schedule, same scratch)
+    if (maps && kv_dtype == VT_KV_FP8_E4M3 && vt::attn_flat_umma_supports(batch, h, kvh, kv_dtype)) {
+      p.maps = maps;
+      return vt::launch_attn_flat_umma(p, s);
+    }
     return vt::launch_attn_flat(p, kv_dtype, s);
   }
   vt::carve_workspace(workspace, batch, h, plan.max_parts, &p);
@@ -349,6 +354,39 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
   return decode_attn_impl(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, batch, h, kvh, d,
                           max_seq_len, scale, kv_dtype, k_scale, v_scale, lse, workspace, workspace_bytes, 0, stream,
                           key, value, key_stride, value_stride, byte_off, flags);
+}
+
+int vt_decode_step_tma(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *key,
+                       const void *value, int64_t key_stride, int64_t value_stride, const int64_t *byte_off,
+                       const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
+                       const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len, float scale,
+                       int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
+                       size_t workspace_bytes, unsigned flags, const void *maps, void *stream) {
+  if (batch < 0 || kvh <= 0 || (flags & ~static_cast<unsigned>(VT_STEP_OVERLAP | VT_STEP_EARLY_KV))) return VT_ERR_INVALID;
+  if (batch == 0) return VT_OK;
+  if (!maps || (reinterpret_cast<uintptr_t>(maps) & 63) != 0) return VT_ERR_INVALID;
+  if (key || value) {
+    if (!key || !value || !byte_off) return VT_ERR_INVALID;
+    if ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 15) return VT_ERR_INVALID;
+    if ((key_stride % 8) || (value_stride % 8) || key_stride < static_cast<int64_t>(kvh) * d ||
+        value_stride < static_cast<int64_t>(kvh) * d)
+      return VT_ERR_INVALID;
+  } else if (flags) {
+    return VT_ERR_INVALID;   // the overlap forms are defined for the fused step only
+  }
+  return decode_attn_impl(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, batch, h, kvh, d,
+                          max_seq_len, scale, kv_dtype, k_scale, v_scale, lse, workspace, workspace_bytes, 0, stream,
+                          key, value, key_stride, value_stride, byte_off, flags, maps);
+}
+
+int vt_decode_maps_encode(const uint64_t *k_bases, const uint64_t *v_bases, int n_slots, int kvh, int d, int kv_dtype,
+                          uint64_t max_tokens, void *host_maps) {
+  if (!k_bases || !v_bases || !host_maps || n_slots <= 0 || kvh <= 0 || max_tokens == 0) return VT_ERR_INVALID;
+  if ((reinterpret_cast<uintptr_t>(host_maps) & 63) != 0) return VT_ERR_INVALID;
+  if (d != vt::kHeadDim || kv_dtype != VT_KV_FP8_E4M3) return VT_ERR_UNSUPPORTED;
+  // whole 32-token boxes are fetched at the ragged end of a context: a box must not straddle a 2 MiB chunk
+  if ((kvh & (kvh - 1)) != 0 || kvh * 32 > 8192 || max_tokens > 0xffffffffull) return VT_ERR_UNSUPPORTED;
+  return vt::encode_decode_maps_f8(k_bases, v_bases, n_slots, kvh, max_tokens, host_maps);
 }
 
 static int prefill_impl(void *out, int64_t out_stride, const void *q, int64_t q_stride, const uint64_t *k_table,

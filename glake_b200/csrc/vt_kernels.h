@@ -73,6 +73,7 @@ struct AttnParams {
   const void *new_key, *new_value;    // bf16 [batch, kvh, 128]; nullptr = plain attention
   int64_t new_key_stride, new_value_stride;   // elements per batch row
   const int64_t *byte_off;            // destination byte offset per entry (negative = nothing to append)
+  const void *maps;                   // tcgen05 engine only: device table [slot][K, V] of 128-byte TMA tensor maps
   int overlap;                        // launched as a programmatic dependent of the previous kernel on the stream:
                                       // 1 = its inputs are ready already, 2 = wait for that kernel before reading q / new rows
 };
@@ -121,5 +122,10 @@ bool attn_flat_supports(int batch, int h, int kvh, int kv_dtype);
 int flat_consumer_warps(int kv_dtype);
 int flat_max_ctas(int h, int kvh, int kv_dtype);
 int launch_attn_reduce(const AttnParams &p, int kv_dtype, cudaStream_t stream);
+// fp8 cache on tcgen05 (same schedule and scratch as the flat kernel); needs p.maps from encode_decode_maps_f8
+int launch_attn_flat_umma(const AttnParams &p, cudaStream_t stream);
+bool attn_flat_umma_supports(int batch, int h, int kvh, int kv_dtype);
+int encode_decode_maps_f8(const uint64_t *k_bases, const uint64_t *v_bases, int n_slots, int kvh, uint64_t max_tokens,
+                          void *host_maps);
 
 }  // namespace vt

@@ -154,9 +154,18 @@ def kv_scales(x, num_kv_heads, head_size):
 
 
 def _decode(out, query, k_table, v_table, num_kv_heads, scale, seq_lens, max_seq_len, slot_ids, kv_dtype,
-            k_scale, v_scale, lse, num_splits):
+            k_scale, v_scale, lse, num_splits, maps=None):
     batch, num_heads, head_size = query.shape
     ws = attn_workspace(query.device, batch, num_heads, head_size, max_seq_len)
+    if maps is not None and num_splits == 0:
+        # plain attention through the tensor-map entry point (no rows to append)
+        with torch.cuda.device(query.device):
+            check(lib.vt_decode_step_tma(_ptr(out), out.stride(0), _ptr(query), query.stride(0), None, None, 0, 0, None,
+                                         c_void_p(int(k_table)), c_void_p(int(v_table)), _ptr(slot_ids), _ptr(seq_lens),
+                                         batch, num_heads, num_kv_heads, head_size, int(max_seq_len), float(scale),
+                                         kv_dtype, _ptr(k_scale), _ptr(v_scale), _ptr(lse), _ptr(ws), ws.numel(), 0,
+                                         _ptr(maps), _stream()), "vt_decode_step_tma")
+        return
     with torch.cuda.device(query.device):
         check(lib.vt_decode_attn(_ptr(out), out.stride(0), _ptr(query), query.stride(0), c_void_p(int(k_table)),
                                  c_void_p(int(v_table)), _ptr(slot_ids), _ptr(seq_lens), batch, num_heads,
@@ -167,12 +176,13 @@ def _decode(out, query, k_table, v_table, num_kv_heads, scale, seq_lens, max_seq
 
 def paged_attention_v1(out, query, key_cache, value_cache, num_kv_heads, scale, seq_lens, block_size, max_seq_len,
                        alibi_slopes, kv_cache_dtype, kv_scale, slot_mapping, k_scale=None, v_scale=None,
-                       num_splits=0):
+                       num_splits=0, maps=None):
     """Decode attention with the reference's vTensor signature (csrc/ops.h:6-19):
     ``key_cache`` / ``value_cache`` are the device addresses (ints) of the per-layer
     pointer tables, ``slot_mapping`` the slot ids.  ``block_size`` must be 1 (the
-    token-major contiguous layout, vllm/attention/ops/paged_attn.py:105)."""
-    _require_cuda(out, query, seq_lens, slot_mapping)
+    token-major contiguous layout, vllm/attention/ops/paged_attn.py:105).  ``maps`` (from
+    :func:`decode_maps`, fp8 cache) selects the tcgen05 kernel where the head counts allow."""
+    _require_cuda(out, query, seq_lens, slot_mapping, maps)
     if alibi_slopes is not None:
         raise RuntimeError("paged_attention_v1: ALiBi is not supported on the vTensor path")
     if block_size != 1:
@@ -184,7 +194,7 @@ def paged_attention_v1(out, query, key_cache, value_cache, num_kv_heads, scale, 
         k_scale = torch.full((num_kv_heads,), float(kv_scale), dtype=torch.float32, device=query.device)
         v_scale = k_scale
     _decode(out, query, key_cache, value_cache, num_kv_heads, scale, seq_lens, max_seq_len, slot_mapping, kvd,
-            k_scale, v_scale, None, num_splits)
+            k_scale, v_scale, None, num_splits, maps)
 
 
 def fwd_kvcache(q, k_table_ptr, v_table_ptr, max_seq_len, num_kv_heads, batch, slot_mapping, k_new, v_new,
@@ -230,7 +240,7 @@ def fwd_kvcache(q, k_table_ptr, v_table_ptr, max_seq_len, num_kv_heads, batch, s
 
 def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_mapping, seq_lens, max_seq_len,
                 num_kv_heads, scale, kv_cache_dtype="auto", k_scale=None, v_scale=None, lse=None, overlap=False,
-                workspace=None):
+                workspace=None, maps=None):
     """``reshape_and_cache`` (decode form) + ``paged_attention_v1`` in one call; one
     kernel launch for a bf16 cache.  ``key_cache`` / ``value_cache`` are the device
     addresses of the layer's pointer tables (ints), ``slot_m`` the destination byte
@@ -240,8 +250,10 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
     stream (VT_STEP_OVERLAP): only for a different layer's ranges, see vtensor.h;
     ``overlap="early_kv"`` (VT_STEP_EARLY_KV) is the form for inputs that the preceding
     kernel produces: cache rows stream early, q / key / value are read after it finished.
-    Pass a private zero-filled ``workspace`` (uint8 tensor) in both cases."""
-    _require_cuda(out, query, key, value, slot_m, slot_mapping, seq_lens)
+    Pass a private zero-filled ``workspace`` (uint8 tensor) in both cases.
+    ``maps`` (from :func:`decode_maps`, fp8 cache only) selects the tcgen05 kernel where
+    the head counts allow; other shapes run as without it."""
+    _require_cuda(out, query, key, value, slot_m, slot_mapping, seq_lens, maps)
     batch, num_heads, head_size = query.shape
     key = key.view(batch, num_kv_heads, head_size)
     value = value.view(batch, num_kv_heads, head_size)
@@ -249,13 +261,22 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
         raise RuntimeError("decode_step(overlap=True) needs a private zero-filled workspace")
     ws = workspace if workspace is not None else attn_workspace(query.device, batch, num_heads, head_size,
                                                                 max_seq_len)
+    flags = 2 if overlap == "early_kv" else (1 if overlap else 0)
+    if maps is not None:
+        with torch.cuda.device(query.device):
+            check(lib.vt_decode_step_tma(_ptr(out), out.stride(0), _ptr(query), query.stride(0), _ptr(key), _ptr(value),
+                                         key.stride(0), value.stride(0), _ptr(slot_m), c_void_p(int(key_cache)),
+                                         c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens), batch,
+                                         num_heads, num_kv_heads, head_size, int(max_seq_len), float(scale),
+                                         _kv_dtype(kv_cache_dtype), _ptr(k_scale), _ptr(v_scale), _ptr(lse), _ptr(ws),
+                                         ws.numel(), flags, _ptr(maps), _stream()), "vt_decode_step_tma")
+        return
     with torch.cuda.device(query.device):
         check(lib.vt_decode_step(_ptr(out), out.stride(0), _ptr(query), query.stride(0), _ptr(key), _ptr(value),
                                  key.stride(0), value.stride(0), _ptr(slot_m), c_void_p(int(key_cache)),
                                  c_void_p(int(value_cache)), _ptr(slot_mapping), _ptr(seq_lens), batch, num_heads,
                                  num_kv_heads, head_size, int(max_seq_len), float(scale), _kv_dtype(kv_cache_dtype),
-                                 _ptr(k_scale), _ptr(v_scale), _ptr(lse), _ptr(ws), ws.numel(),
-                                 2 if overlap == "early_kv" else (1 if overlap else 0), _stream()),
+                                 _ptr(k_scale), _ptr(v_scale), _ptr(lse), _ptr(ws), ws.numel(), flags, _stream()),
               "vt_decode_step")
 
 
@@ -283,6 +304,28 @@ def prefill_maps(k_bases, v_bases, num_kv_heads, head_size, max_tokens, device):
     with torch.cuda.device(device):
         check(lib.vt_prefill_maps_encode(kb, vb, n, num_kv_heads, head_size, int(max_tokens),
                                          c_void_p(host.data_ptr() + off)), "vt_prefill_maps_encode")
+    return host[off: off + n * 256].to(device)
+
+
+def decode_tma_supported(num_heads, num_kv_heads, kv_cache_dtype):
+    """Whether ``decode_step(..., maps=...)`` runs the tcgen05 kernel for this shape (fp8 cache,
+    kv heads a power of two >= 8, at most 4 q heads per kv head); other shapes ignore the maps."""
+    g = num_heads // num_kv_heads
+    return (_kv_dtype(kv_cache_dtype) == VT_KV_FP8_E4M3 and num_kv_heads % 8 == 0
+            and num_kv_heads & (num_kv_heads - 1) == 0 and num_kv_heads <= 256 and g in (1, 2, 4))
+
+
+def decode_maps(k_bases, v_bases, num_kv_heads, head_size, max_tokens, device, kv_cache_dtype="fp8"):
+    """Device table of TMA tensor maps for ``decode_step(..., maps=...)`` over fp8 ranges:
+    ``k_bases[i]`` / ``v_bases[i]`` are slot i's range bases of one layer.  Valid while the slots live."""
+    n = len(k_bases)
+    kb = (ctypes.c_uint64 * n)(*[int(x) for x in k_bases])
+    vb = (ctypes.c_uint64 * n)(*[int(x) for x in v_bases])
+    host = torch.empty(n * 256 + 64, dtype=torch.uint8)
+    off = (-host.data_ptr()) % 64
+    with torch.cuda.device(device):
+        check(lib.vt_decode_maps_encode(kb, vb, n, num_kv_heads, head_size, _kv_dtype(kv_cache_dtype), int(max_tokens),
+                                        c_void_p(host.data_ptr() + off)), "vt_decode_maps_encode")
     return host[off: off + n * 256].to(device)
 
 

@@ -291,6 +291,32 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
                    int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
                    size_t workspace_bytes, unsigned flags, void *stream);
 
+/* vt_decode_step for an fp8 cache with the K/V tiles fetched by TMA tensor copies and
+ * the two products on tcgen05.mma.kind::f8f6f4 (the cache bytes reach the tensor core
+ * unconverted; Q is carried as two and P as three e4m3 terms).  Same arguments and
+ * results within the fp8 tolerance of vt_decode_step, plus
+ *   maps   device copy of the table vt_decode_maps_encode filled: for every slot id a
+ *          K and a V tensor map of this layer's ranges (2 x 128 bytes per slot,
+ *          64-byte aligned).
+ * key / value may both be NULL (plain attention over rows already appended; flags
+ * must then be 0).  Shapes the tcgen05 kernel does not take (kv heads not a power of
+ * two >= 8, more than 4 q heads per kv head, bf16 ranges) run exactly as vt_decode_step.
+ * vt_decode_maps_encode writes the table into HOST memory (n_slots x 256 bytes, 64-byte
+ * aligned; the caller copies it to the device once): k_bases / v_bases are the slots'
+ * range bases of one layer, max_tokens the rows a range is reserved for.  Bases never
+ * move, so the table stays valid while the slots live.  kv_dtype must be
+ * VT_KV_FP8_E4M3 and kvh a power of two <= 256 (VT_ERR_UNSUPPORTED otherwise).
+ * No counterpart in the reference (its fp8 decode is paged_attention_v1/v2 with
+ * per-element conversion, csrc/attention/attention_kernels.cu:93-420). */
+int vt_decode_maps_encode(const uint64_t *k_bases, const uint64_t *v_bases, int n_slots, int kvh, int d,
+                          int kv_dtype, uint64_t max_tokens, void *host_maps);
+int vt_decode_step_tma(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *key,
+                       const void *value, int64_t key_stride, int64_t value_stride, const int64_t *byte_off,
+                       const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,
+                       const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len, float scale,
+                       int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
+                       size_t workspace_bytes, unsigned flags, const void *maps, void *stream);
+
 /* Causal attention of the NEW tokens of each sequence over its whole range
  * (prefix + new tokens; the new rows must have been appended with vt_append):
  * query row j of entry i sits at position seq_lens[i] - q_lens[i] + j and attends
