@@ -214,16 +214,18 @@ class VTensorAttentionImpl:
             raise ValueError("head size 128 only")
 
     def forward(self, query, key, value, key_cache: KV_cache, value_cache: KV_cache, attn_metadata: VTensorMetadata,
-                kv_scale: float = 1.0, k_scale=None, v_scale=None, prefill_maps=None):
+                kv_scale: float = 1.0, k_scale=None, v_scale=None, prefill_maps=None, decode_maps=None):
         """query ``[tokens, H*D]``, key/value ``[tokens, KVH*D]`` -> ``[tokens, H*D]``.
         ``prefill_maps``: the layer's tensor-map table (``VTensorCacheEngine.prefill_maps``),
-        used by the prompt branch when given.  ``k_scale`` / ``v_scale``: the layer's per-kv-head
+        used by the prompt branch when given; ``decode_maps``: the one of an fp8 cache for the
+        decode branch (``VTensorCacheEngine.decode_maps``: the tcgen05 kernel).  ``k_scale`` / ``v_scale``: the layer's per-kv-head
         scales of an fp8 cache (``ops.kv_scales`` of the first prompt's rows, then frozen)."""
         with nvtx_range("vtensor attention: prompt" if attn_metadata.num_prefills > 0 else "vtensor attention: decode"):
             return self._forward(query, key, value, key_cache, value_cache, attn_metadata, k_scale, v_scale,
-                                 prefill_maps)
+                                 prefill_maps, decode_maps)
 
-    def _forward(self, query, key, value, key_cache, value_cache, attn_metadata, k_scale, v_scale, prefill_maps):
+    def _forward(self, query, key, value, key_cache, value_cache, attn_metadata, k_scale, v_scale, prefill_maps,
+                 decode_maps=None):
         query = query.view(-1, self.num_heads, self.head_size)
         key = key.view(-1, self.num_kv_heads, self.head_size)
         value = value.view(-1, self.num_kv_heads, self.head_size)
@@ -250,7 +252,7 @@ class VTensorAttentionImpl:
         output = torch.empty_like(query)
         ops.decode_step(output, query, key, value, key_cache.vmm_ptr, value_cache.vmm_ptr, m.slot_m, m.slot_mapping,
                         m.seq_lens_tensor, m.max_seq_len, self.num_kv_heads, self.scale, self.kv_cache_dtype,
-                        k_scale, v_scale)
+                        k_scale, v_scale, maps=decode_maps)
         return output.view(-1, self.num_heads * self.head_size)
 
 

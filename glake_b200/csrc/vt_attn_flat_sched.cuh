@@ -29,6 +29,7 @@ struct Piece {
 
 // Locates the stream holding position `tau` and the run of tiles this CTA owns inside
 // it.  prefix[b] = position of sequence b's first stream.
+template <int kCost = kBoundaryCost>
 __device__ __forceinline__ Piece locate(const int *prefix, int batch, int slabs, long long tau, long long tau_end) {
   int lo = 0, hi = batch;  // largest b with prefix[b] <= tau
   while (hi - lo > 1) {
@@ -41,13 +42,13 @@ __device__ __forceinline__ Piece locate(const int *prefix, int batch, int slabs,
   const int rem = static_cast<int>(tau - prefix[lo]);
   pc.slab = rem / per_slab;
   const int pos = rem % per_slab;
-  pc.tiles_in_stream = per_slab - kBoundaryCost;
+  pc.tiles_in_stream = per_slab - kCost;
   pc.stream_begin = prefix[lo] + static_cast<long long>(pc.slab) * per_slab;
   pc.stream_end = pc.stream_begin + per_slab;
   const int end = static_cast<int>(min(static_cast<long long>(per_slab), pos + (tau_end - tau)));
   pc.advance = end - pos;
-  pc.tile_begin = max(pos - kBoundaryCost, 0);
-  pc.tile_end = max(end - kBoundaryCost, 0);
+  pc.tile_begin = max(pos - kCost, 0);
+  pc.tile_end = max(end - kCost, 0);
   return pc;
 }
 
@@ -60,7 +61,10 @@ __device__ __forceinline__ int owner_of(long long tau, long long total, int n_ct
 // own piece and passed a CTA-wide barrier; every consumer warp of the CTA calls this.
 // kCWarps / HS / R / HEADS describe the scratch layout ([cta][2 slots][kCWarps][HEADS] rows;
 // consumer warp r * HS + hh holds kv head hh of the slab), kFp8 applies the V scale.
-template <int kCWarps, int HS, int R, int HEADS, bool kFp8>
+// kFold: pieces that were their CTA's last piece were folded to one row per head before they
+// were published (the mma.sync kernel does that in its idle ring); without it every piece
+// arrives as R rows per head.
+template <int kCWarps, int HS, int R, int HEADS, bool kFp8, bool kFold = true>
 __device__ __forceinline__ void merge_stream(const AttnParams &p, const Piece &pc, long long total, int n_ctas,
                                              int c_first, int c_last, int warp, int lane, int g) {
   const long long s_begin = pc.stream_begin, s_end = pc.stream_end;
@@ -75,8 +79,8 @@ __device__ __forceinline__ void merge_stream(const AttnParams &p, const Piece &p
   // Pieces that were their CTA's last piece arrive folded (one row per head):
   // that is every piece but, possibly, the one in the stream's last CTA.
   const bool last_folded = R == 1 || total * (c_last + 1) / n_ctas <= s_end + kBoundaryCost;
-  const int n_single = last_folded ? n_pieces : n_pieces - 1;
-  const int n_src = R == 1 ? n_pieces : n_single + (last_folded ? 0 : R);
+  const int n_single = !kFold ? 0 : last_folded ? n_pieces : n_pieces - 1;
+  const int n_src = R == 1 ? n_pieces : !kFold ? n_pieces * R : n_single + (last_folded ? 0 : R);
   for (int item = warp; item < HS * g; item += kCWarps) {
     const int hh = item / g, head = item % g;
     float M = -INFINITY, L = 0.f;
@@ -86,8 +90,8 @@ __device__ __forceinline__ void merge_stream(const AttnParams &p, const Piece &p
       const float *mine = nullptr;
       float mi = -INFINITY, li = 0.f;
       if (i < n_src) {
-        const int c = i < n_single ? c_first + i : c_last;
-        const int r = i < n_single ? 0 : i - n_single;
+        const int c = !kFold ? c_first + i / R : i < n_single ? c_first + i : c_last;
+        const int r = !kFold ? i % R : i < n_single ? 0 : i - n_single;
         // the stream is CTA c's first piece iff it already runs at c's first tile
         const int sl = (s_begin <= total * c / n_ctas) ? 0 : 1;
         mine = p.fl_part + (((static_cast<size_t>(c) * 2 + sl) * kCWarps + r * HS + hh) * HEADS + head) * kPartRow;

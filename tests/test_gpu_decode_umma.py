@@ -74,3 +74,86 @@ def test_fused_steps_match_oracle_and_cache_bytes(G, oracle, h, kvh):
             assert float((lse - lse_ref).abs().max()) <= 2e-2
     finally:
         kv.close()
+
+
+def _attend(kv, q, maps, h):
+    from glake_b200 import ops
+    qd = q.cuda()
+    out = torch.empty_like(qd)
+    ops.paged_attention_v1(out, qd, kv.k_table, kv.v_table, kv.kvh, SCALE, kv.meta.seq_lens_tensor, 1,
+                           kv.meta.max_seq_len, None, "fp8_e4m3", 1.0, kv.meta.slot_mapping, k_scale=kv.k_scale,
+                           v_scale=kv.v_scale, maps=maps)
+    torch.cuda.synchronize()
+    assert ops.attn_status() == 0
+    return out.cpu()
+
+
+def test_full_context_golden_with_scales_from_the_prefill_append(G, oracle):
+    """Config-4 shape (32 q / 8 kv heads, contexts up to 8k) on real data: against the committed
+    output of the reference's CPU kernel over a bf16 cache (<= 3e-2) and against the fp8
+    restatement (<= 1e-2); scales amax / 448 over the prefill rows, frozen."""
+    from glake_b200 import ops
+    from tests.test_oracle import load_golden
+    name = "fp8_ctx_gqa4_8k"
+    _, gold16 = load_golden(name)
+    seed, lens, h, kvh = synth.golden_lens(name)
+    assert ops.decode_tma_supported(h, kvh, "fp8_e4m3")
+    q, k, v = synth.make_case(seed, lens, h, kvh)
+    ks = ops.kv_scales(torch.cat([x[:-1] for x in k]).cuda(), kvh, 128)
+    vs = ops.kv_scales(torch.cat([x[:-1] for x in v]).cuda(), kvh, 128)
+    kv = G.GpuKV(k, v, kvh, fp8=True, k_scale=ks, v_scale=vs)
+    try:
+        r8 = oracle.fill_ranges(k, v, k_scale=ks.cpu(), v_scale=vs.cpu())
+        port8 = oracle.port_decode_attn(q, r8, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32), kvh,
+                                        SCALE, ks.cpu(), vs.cpu())
+        o8 = _attend(kv, q, kv.engine.decode_maps(0, h), h)
+        assert float((o8.float() - gold16.float()).abs().max()) <= 3e-2
+        assert float((o8.float() - port8.float()).abs().max()) <= 1e-2
+    finally:
+        kv.close()
+
+
+@pytest.mark.parametrize("h,kvh", [(16, 8), (16, 16)])
+def test_many_short_streams_per_cta(G, oracle, h, kvh):
+    """Around a thousand contexts of 1..150 tokens: every CTA walks through several whole streams
+    (each published to and merged from the same scratch slot, both consumer sets, streams of a
+    single tile leave one set empty), identical results on identical calls."""
+    from glake_b200 import ops
+    rs = np.random.RandomState(6160 + h + kvh)
+    lens = [int(x) for x in rs.randint(1, 151, size=1000)]
+    q, k, v = synth.make_case(950 + h + kvh, lens, h, kvh)
+    ks = ops.kv_scales(torch.cat(k).cuda(), kvh, 128)
+    vs = ops.kv_scales(torch.cat(v).cuda(), kvh, 128)
+    kv = G.GpuKV(k, v, kvh, fp8=True, k_scale=ks, v_scale=vs)
+    try:
+        maps = kv.engine.decode_maps(0, h)
+        outs = [_attend(kv, q, maps, h) for _ in range(3)]
+        assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2]), "results differ between identical calls"
+        r = oracle.fill_ranges(k, v, k_scale=ks.cpu(), v_scale=vs.cpu())
+        port = oracle.port_decode_attn(q, r, torch.arange(len(lens)), torch.tensor(lens, dtype=torch.int32), kvh, SCALE,
+                                       ks.cpu(), vs.cpu())
+        ok, err = _tol_ok(outs[0], port)
+        assert ok, err
+    finally:
+        kv.close()
+
+
+def test_shapes_the_kernel_does_not_take_run_as_without_maps(G, oracle):
+    """8 q heads per kv head is outside the tcgen05 kernel's shapes: the engine hands out no maps and
+    the entry point, given maps of another shape's table, falls back to the mma.sync kernel."""
+    from glake_b200 import ops
+    assert not ops.decode_tma_supported(64, 8, "fp8_e4m3") and not ops.decode_tma_supported(32, 8, "auto")
+    assert not ops.decode_tma_supported(8, 4, "fp8_e4m3")
+    lens = [40, 700]
+    q, k, v = synth.make_case(77, lens, 64, 8)
+    ks = ops.kv_scales(torch.cat(k).cuda(), 8, 128)
+    vs = ops.kv_scales(torch.cat(v).cuda(), 8, 128)
+    kv = G.GpuKV(k, v, 8, fp8=True, k_scale=ks, v_scale=vs)
+    try:
+        assert kv.engine.decode_maps(0, 64) is None
+        maps = kv.engine.decode_maps(0, 32)          # a valid table for these ranges; the 64-head call must ignore it
+        got = _attend(kv, q, maps, 64)
+        ref = _attend(kv, q, None, 64)
+        assert torch.equal(got, ref)
+    finally:
+        kv.close()
