@@ -559,7 +559,9 @@ def op_record(name, seed, calls, peak, with_cpu=False):
             rec = {"workload": WORKLOAD_TEXT[name], "calls": n_calls, "ms_per_call": round(ms, 5),
                    "algorithmic_bytes_per_call": int(attn_b), "GB/s": round(gbs, 1),
                    "frac": round(gbs / peak, 4), "pct_of_nominal_8TBs": round(gbs / 80.0, 1),
-                   "kernel": ["simt split-k", "tensor-core split-k", "tensor-core flat persistent"][variant]
+                   "kernel": ("tcgen05.mma kind::f8f6f4 flat persistent (TMA tensor copies, S/O in tensor memory)"
+                              if variant == 2 and job.engine.decode_maps(0, h) is not None else
+                              ["simt split-k", "tensor-core split-k", "mma.sync flat persistent"][variant])
                              + (", fused append" if variant == 2 and ops.step_is_fused(job.dtype) else ", separate append kernel"),
                    "gpu_launches": n_calls, "kernel_status": status,
                    "how": f"CUDA graphs of {per_graph} calls back to back, CUDA events around {replays} replays",

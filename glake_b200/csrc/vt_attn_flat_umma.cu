@@ -63,8 +63,10 @@ constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0;                 // S^T buffer b, half hf: columns [64 b + 32 hf, + 32)
 constexpr uint32_t kColO = 128;               // O^T of consumer set b, kv head j: columns [128 + 128 b + 16 j, + 16)
 // Phantom positions per stream in the cost-balanced split: a stream boundary stalls the consumers
-// (publish, ticket, possibly merge) for about as long as four 64 KiB tiles take to stream.
-constexpr int kUCost = 4;
+// (publish, ticket, possibly merge) for longer than the four or five tiles its own work takes: the producers wait for the stream's last tile
+// to land before they patch it, and the CTA that ends a stream usually merges it.  Measured per
+// boundary: 14 us against 1.25 us per 64 KiB tile; costs of 4 to 16 tiles time alike (within 1 %).
+constexpr int kUCost = 8;
 constexpr float kPScale = 256.f;              // P is carried as 256 p: e4m3 then resolves 2^-17 of the largest term
 
 // offsets from the 1024-byte aligned base of the dynamic shared memory
