@@ -70,6 +70,32 @@ def test_prefill_map_argument_checks():
     assert lib.vt_prefill_attn(*args, None) == VT_ERR_UNSUPPORTED                                 # q rows are read 16 bytes at a time
 
 
+def test_decode_map_argument_checks():
+    """vt_decode_maps_encode / vt_decode_step_tma (the tcgen05 decode path of an fp8 cache): argument
+    errors come back as status codes before anything touches a GPU."""
+    bases = (ctypes.c_uint64 * 2)(1 << 30, 2 << 30)
+    host = P(A16)
+    assert lib.vt_decode_maps_encode(bases, bases, 2, 8, 128, VT_KV_BF16, 4096, host) == VT_ERR_UNSUPPORTED       # fp8 ranges only
+    assert lib.vt_decode_maps_encode(bases, bases, 2, 6, 128, VT_KV_FP8_E4M3, 4096, host) == VT_ERR_UNSUPPORTED   # 6 kv heads
+    assert lib.vt_decode_maps_encode(bases, bases, 2, 8, 64, VT_KV_FP8_E4M3, 4096, host) == VT_ERR_UNSUPPORTED
+    assert lib.vt_decode_maps_encode(bases, bases, 2, 8, 128, VT_KV_FP8_E4M3, 0, host) == VT_ERR_INVALID
+    assert lib.vt_decode_maps_encode(bases, bases, 2, 8, 128, VT_KV_FP8_E4M3, 4096, P(A16 + 8)) == VT_ERR_INVALID # 64-byte aligned table
+    assert lib.vt_decode_maps_encode(None, bases, 2, 8, 128, VT_KV_FP8_E4M3, 4096, host) == VT_ERR_INVALID
+    # out, stride, q, stride, key, value, strides, byte_off, tables, slot ids, seq lens, batch, h, kvh, d, max len, scale, dtype, scales, lse, ws, bytes, flags
+    args = [P(A16), 1024, P(A16), 1024, P(A16), P(A16), 1024, 1024, P(A16), P(A16), P(A16), P(A16), P(A16), 1, 8, 8, 128, 64,
+            0.1, VT_KV_FP8_E4M3, P(A16), P(A16), None, P(A16), 1 << 20, 0]
+    assert lib.vt_decode_step_tma(*args, None, None) == VT_ERR_INVALID                       # maps required
+    assert lib.vt_decode_step_tma(*args, P(A16 + 8), None) == VT_ERR_INVALID                 # 64-byte aligned table
+    bad = list(args); bad[25] = 4
+    assert lib.vt_decode_step_tma(*bad, P(A16), None) == VT_ERR_INVALID                      # unknown flag
+    bad = list(args); bad[4] = None; bad[5] = None; bad[25] = 1
+    assert lib.vt_decode_step_tma(*bad, P(A16), None) == VT_ERR_INVALID                      # overlap forms need the fused step
+    bad = list(args); bad[5] = None
+    assert lib.vt_decode_step_tma(*bad, P(A16), None) == VT_ERR_INVALID                      # key without value
+    bad = list(args); bad[16] = 64
+    assert lib.vt_decode_step_tma(*bad, P(A16), None) == VT_ERR_UNSUPPORTED                  # head size
+
+
 def test_python_ops_refuse_cpu_tensors():
     from glake_b200 import ops
     x = torch.zeros(2, 64, dtype=torch.bfloat16)
