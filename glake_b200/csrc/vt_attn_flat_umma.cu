@@ -4,15 +4,14 @@
 // thread.  Same persistent schedule, scratch format and merge as the mma.sync kernel
 // of vt_attn_flat.cu (pieces, tickets, last CTA of a stream merges); the engine differs.
 //
-// Shapes: kv heads a multiple of 8 (one CTA streams 8 kv heads = 1 KiB token rows),
+// Shapes: kv heads a power of two >= 8 (one CTA streams a slab of 8 kv heads = 1 KiB of every token row),
 // 1, 2 or 4 q heads per kv head, head size 128.  Needs the per-slot TMA tensor maps
 // of encode_decode_maps_f8: a tile is 32 tokens x 8 kv heads, fetched as sixteen
 // 128-byte-swizzled boxes (32 tokens x 128 bytes of one kv head; K, then V).
 //
 // One CTA per SM, nineteen warps:
 //   warps 16, 17  producers of K and of V: tensor copies into a 3-stage ring (2 x 32 KiB per stage,
-//            handed over separately).  The last
-//            tile of a stream is patched by these warps before it is handed on: V rows past
+//            handed over separately).  The last tile of a stream is patched by these warps before it is handed on: V rows past
 //            the context are cleared (0 x NaN would poison the product) and, in a fused
 //            step, this step's K / V row is quantised into the stage and into the range.
 //   warp 18  one lane issues the MMAs.
