@@ -125,6 +125,18 @@ __device__ __forceinline__ float ex2_approx(float x) {      // 2^x, one MUFU op;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Non-blocking look at an mbarrier phase (mbar_wait's try_wait may suspend the thread for a while).
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // The four most significant bits of x as a float (truncated, so the remainder keeps x's
 // sign): an e4m3 value whenever 2^-6 <= |x| < 480.  Smaller x go to the remainder whole.
 __device__ __forceinline__ float top4(float x) {
@@ -285,59 +297,85 @@ __global__ void __launch_bounds__(kUThreads, 1) attn_flat_umma_f8_kernel(AttnPar
     if (!ok && lane == 0) *failed = 1;
   } else if (warp == kUCWarps + 2) {
     // ---------------- MMA issuer ----------------
+    // One lane issues both kinds of product, whichever is ready: S^T of the next tile needs its K tile,
+    // a free S^T buffer and (at a stream's first tile) the new Q; O^T of the oldest tile without one
+    // needs its V tile, its P and a free O^T buffer.  Neither waits behind the other (a P.V product
+    // queued behind the next tile's K would keep its V stage, and the consumers, waiting), so the
+    // barriers are polled, not waited on; a second without any progress fails the launch.
     if (lane == 0) {
       const uint32_t idesc_qk = umma_idesc_e4m3_f32(128, 32, false, false);
       const uint32_t idesc_pv = umma_idesc_e4m3_f32(128, 16, true, false);
       bool ok = true;
-      int it = 0, pieces = 0;
-      // O^T of tile i (all 8 kv heads) into the O columns of its consumer set; releases the tile's ring stage
-      auto issue_pv = [&](int i) -> bool {
-        const int b = i & 1, s = i % kUStages;
-        if (!mbar_wait(v_full + 8 * s, (i / kUStages) & 1)) return false;            // V of tile i has landed
-        if (!mbar_wait(p_full + 8 * b, (i >> 1) & 1)) return false;                  // P of tile i is in shared memory
-        if (i >= 2 && !mbar_wait(o_free + 8 * b, ((i >> 1) - 1) & 1)) return false;  // the set read O^T of its previous tile
-        tcgen05_fence_after();
-        const uint32_t vst = ring_s + s * kUStageB + kKVTileB;
+      int qk_it = 0, pv_it = 0, pieces = 0;      // tiles whose S^T / O^T product has been issued; streams begun
+      long long tau = tau0;
+      Piece pc{};
+      int tile = 0;                              // next tile of pc (tile == pc.tile_end: fetch the next piece)
+      bool have_q = false;                       // the current piece's Q operand has been seen ready
+      unsigned long long idle_since = 0;
+      for (;;) {
+        bool progress = false;
+        // ---- O^T of tile pv_it ----
+        if (pv_it < qk_it) {
+          const int i = pv_it, b = i & 1, s = i % kUStages;
+          if (mbar_test(v_full + 8 * s, (i / kUStages) & 1) && mbar_test(p_full + 8 * b, (i >> 1) & 1) &&
+              (i < 2 || mbar_test(o_free + 8 * b, ((i >> 1) - 1) & 1))) {
+            tcgen05_fence_after();
+            const uint32_t vst = ring_s + s * kUStageB + kKVTileB;
 #pragma unroll
-        for (int j = 0; j < kUHS; ++j) {
-          const uint64_t da = umma_desc_sw128(vst + j * kHeadTileB, 0, 1024);                           // 32 tokens x 128 dims
-          const uint64_t db = umma_desc_sw128(p_s + (b * 2 + (j >> 2)) * kPSlabB + (j & 3) * 32, 0, 1024);
-          umma_f8(tmem + kColO + b * 128 + j * 16, da, db, idesc_pv, false);
-        }
-        umma_commit(o_full + 8 * b);
-        umma_commit(v_empty + 8 * s);
-        return true;
-      };
-      for (long long tau = tau0; ok && tau < tau1;) {
-        const Piece pc = locate<kUCost>(prefix, p.batch, slabs, tau, tau1);
-        tau += pc.advance;
-        if (pc.tile_end <= pc.tile_begin) continue;
-        // A new stream brings a new Q, which set 0 writes once it is through with the previous
-        // stream's tiles: that stream's last product must be on its way before this thread waits.
-        if (it > 0 && !issue_pv(it - 1)) { ok = false; break; }
-        const int qbuf = pieces & 1;                       // Q operands alternate between two buffers
-        if (!mbar_wait(q_ready, pieces & 1)) { ok = false; break; }
-        ++pieces;
-        for (int tile = pc.tile_begin; tile < pc.tile_end; ++tile, ++it) {
-          const int b = it & 1, s = it % kUStages;
-          if (!mbar_wait(k_full + 8 * s, (it / kUStages) & 1)) { ok = false; break; }
-          if (it >= 2 && !mbar_wait(s_free + 8 * b, ((it >> 1) - 1) & 1)) { ok = false; break; }
-          tcgen05_fence_after();
-          const uint32_t kst = ring_s + s * kUStageB;
-#pragma unroll
-          for (int hf = 0; hf < 2; ++hf)
-#pragma unroll
-            for (int ks = 0; ks < 4; ++ks) {
-              const uint64_t da = umma_desc_sw128(kst + hf * 4 * kHeadTileB + ks * 32, 0, 1024);
-              const uint64_t db = umma_desc_sw128(q_s + (qbuf * 2 + hf) * kQSlabB + ks * 32, 0, 1024);
-              umma_f8(tmem + kColS + b * 64 + hf * 32, da, db, idesc_qk, ks > 0);
+            for (int j = 0; j < kUHS; ++j) {
+              const uint64_t da = umma_desc_sw128(vst + j * kHeadTileB, 0, 1024);                           // 32 tokens x 128 dims
+              const uint64_t db = umma_desc_sw128(p_s + (b * 2 + (j >> 2)) * kPSlabB + (j & 3) * 32, 0, 1024);
+              umma_f8(tmem + kColO + b * 128 + j * 16, da, db, idesc_pv, false);
             }
-          umma_commit(s_full + 8 * b);
-          umma_commit(k_empty + 8 * s);
-          if (tile > pc.tile_begin && !issue_pv(it - 1)) { ok = false; break; }
+            umma_commit(o_full + 8 * b);
+            umma_commit(v_empty + 8 * s);         // releases the V half of the ring stage
+            ++pv_it;
+            progress = true;
+          }
+        }
+        // ---- S^T of tile qk_it ----
+        while (tile >= pc.tile_end && tau < tau1) {            // next piece with real tiles
+          pc = locate<kUCost>(prefix, p.batch, slabs, tau, tau1);
+          tau += pc.advance;
+          tile = pc.tile_begin;
+          if (pc.tile_end > pc.tile_begin) {
+            have_q = false;
+            ++pieces;
+          }
+        }
+        const bool more_qk = tile < pc.tile_end;
+        if (more_qk) {
+          const int it = qk_it, b = it & 1, s = it % kUStages;
+          const int qbuf = (pieces - 1) & 1;                   // Q operands alternate between two buffers
+          if (!have_q) have_q = mbar_test(q_ready, (pieces - 1) & 1);
+          if (have_q && mbar_test(k_full + 8 * s, (it / kUStages) & 1) &&
+              (it < 2 || mbar_test(s_free + 8 * b, ((it >> 1) - 1) & 1))) {
+            tcgen05_fence_after();
+            const uint32_t kst = ring_s + s * kUStageB;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf)
+#pragma unroll
+              for (int ks = 0; ks < 4; ++ks) {
+                const uint64_t da = umma_desc_sw128(kst + hf * 4 * kHeadTileB + ks * 32, 0, 1024);
+                const uint64_t db = umma_desc_sw128(q_s + (qbuf * 2 + hf) * kQSlabB + ks * 32, 0, 1024);
+                umma_f8(tmem + kColS + b * 64 + hf * 32, da, db, idesc_qk, ks > 0);
+              }
+            umma_commit(s_full + 8 * b);
+            umma_commit(k_empty + 8 * s);         // releases the K half of the ring stage
+            ++qk_it;
+            ++tile;
+            progress = true;
+          }
+        }
+        if (!more_qk && pv_it == qk_it) break;   // every tile of the share has both products on their way
+        if (progress) {
+          idle_since = 0;
+        } else {
+          const unsigned long long now = global_timer_ns();
+          if (idle_since == 0) idle_since = now;
+          else if (now - idle_since > kWaitLimitNs) { ok = false; break; }
         }
       }
-      if (ok && it > 0 && !issue_pv(it - 1)) ok = false;
       if (!ok) *failed = 1;
     }
   } else {
