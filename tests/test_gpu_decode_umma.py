@@ -157,3 +157,50 @@ def test_shapes_the_kernel_does_not_take_run_as_without_maps(G, oracle):
         assert torch.equal(got, ref)
     finally:
         kv.close()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_batches_with_emptied_sequences(G, oracle, seed):
+    """Randomised batches: piece boundaries, stream merges, fewer tiles than CTAs, more than 256
+    sequences, a few long streams cut into many pieces; then the same batch with every third
+    sequence emptied (zeros there, the others unchanged up to the order of the sums)."""
+    from glake_b200 import ops
+    rs = np.random.RandomState(3000 + seed)
+    kvh = int(rs.choice([8, 16]))
+    g = int(rs.choice([1, 2, 4]))
+    h = kvh * g
+    if seed == 1:
+        batch, hi = 300, 40
+    elif seed == 2:
+        batch, hi = 3, 20000
+    else:
+        batch, hi = int(rs.randint(1, 40)), int(rs.choice([3, 70, 700, 3000]))
+    lens = [int(x) for x in rs.randint(1, hi + 1, size=batch)]
+    q, k, v = synth.make_case(4000 + seed, lens, h, kvh)
+    ks = ops.kv_scales(torch.cat(k).cuda(), kvh, 128)
+    vs = ops.kv_scales(torch.cat(v).cuda(), kvh, 128)
+    kv = G.GpuKV(k, v, kvh, fp8=True, k_scale=ks, v_scale=vs)
+    try:
+        maps = kv.engine.decode_maps(0, h)
+        assert maps is not None
+        out = _attend(kv, q, maps, h)
+        r = oracle.fill_ranges(k, v, k_scale=ks.cpu(), v_scale=vs.cpu())
+        port = oracle.port_decode_attn(q, r, torch.arange(batch), torch.tensor(lens, dtype=torch.int32), kvh, SCALE,
+                                       ks.cpu(), vs.cpu())
+        # the oracle rounds every dequantised element to bf16, the kernel keeps fp8 * scale exact: on
+        # contexts of a few dozen tokens that alone moves outputs by ~1e-2 (the fp8 contract tolerance, 3e-2)
+        err = (out.float() - port.float()).abs()
+        tol = torch.maximum(torch.full_like(err, 3e-2), port.float().abs() * 2.0 ** -6)
+        assert bool((err <= tol).all()), (float((err - tol).max()), lens)
+        ref = _attend(kv, q, None, h)                         # the mma.sync kernel on the same ranges
+        assert float((out.float() - ref.float()).abs().max()) <= 2e-2
+        if batch >= 3:
+            sl = kv.meta.seq_lens_tensor.clone()
+            kv.meta.seq_lens_tensor[::3] = 0
+            out2 = _attend(kv, q, maps, h)
+            kv.meta.seq_lens_tensor.copy_(sl)
+            assert torch.equal(out2[::3], torch.zeros_like(out2[::3]))
+            keep = [i for i in range(batch) if i % 3]
+            assert float((out2[keep].float() - out[keep].float()).abs().max()) <= 4e-3
+    finally:
+        kv.close()
