@@ -83,6 +83,7 @@ __device__ __forceinline__ void merge_stream(const AttnParams &p, const Piece &p
   const int n_src = R == 1 ? n_pieces : !kFold ? n_pieces * R : n_single + (last_folded ? 0 : R);
   for (int item = warp; item < HS * g; item += kCWarps) {
     const int hh = item / g, head = item % g;
+    const float vsc = kFp8 ? __ldg(p.v_scale + pc.slab * HS + hh) : 1.0f;   // in flight with the sources, not after them
     float M = -INFINITY, L = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s0 = 0; s0 < n_src; s0 += 32) {
@@ -139,7 +140,7 @@ __device__ __forceinline__ void merge_stream(const AttnParams &p, const Piece &p
       }
     }
     const int hq = (pc.slab * HS + hh) * g + head;
-    const float inv = (kFp8 ? p.v_scale[pc.slab * HS + hh] : 1.0f) / L;
+    const float inv = vsc / L;
     uint2 packed;
     packed.x = pack_bf16(acc.x * inv, acc.y * inv);
     packed.y = pack_bf16(acc.z * inv, acc.w * inv);
