@@ -525,7 +525,7 @@ def op_record(name, seed, calls, peak, with_cpu=False):
                     ops.decode_step(out[layer], q[layer], k[layer], v[layer], kc.vmm_ptr, vc.vmm_ptr, meta.slot_m,
                                     meta.slot_mapping, meta.seq_lens_tensor, meta.max_seq_len, kvh, D ** -0.5, job.dtype,
                                     job.scale_k[layer] if job.fp8 else None, job.scale_v[layer] if job.fp8 else None,
-                                    workspace=ws, maps=job.engine.decode_maps(layer, h))
+                                    workspace=ws, maps=job.engine.decode_maps(layer, h), clean_scratch=True)
             per_graph = max(1, 20 // job.layers) * job.layers
             side = torch.cuda.Stream(device=job.dev)
             with torch.cuda.stream(side):

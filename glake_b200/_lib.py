@@ -17,6 +17,7 @@ VT_ERR_TOO_LARGE = 11
 VT_STATIC_SCRATCH_BYTES = 24 << 20
 VT_STEP_OVERLAP = 1
 VT_STEP_EARLY_KV = 2
+VT_STEP_CLEAN_SCRATCH = 4
 VT_KV_BF16, VT_KV_FP8_E4M3 = 0, 1
 
 

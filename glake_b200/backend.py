@@ -344,7 +344,7 @@ class DecodeRunner:
                             self.v[layer], kc.vmm_ptr, vc.vmm_ptr, self.d64[:b], self.d64[b:], self.d32[:b],
                             meta.max_seq_len, self.impl.num_kv_heads, self.impl.scale, self.impl.kv_cache_dtype,
                             ks, vs, overlap=self._overlap_mode(layer), workspace=self.workspace,
-                            maps=self.engine.decode_maps(layer, self.impl.num_heads))
+                            maps=self.engine.decode_maps(layer, self.impl.num_heads), clean_scratch=True)
             torch.cuda.nvtx.range_pop()
             if self.post_layer is not None:
                 self.post_layer(layer)

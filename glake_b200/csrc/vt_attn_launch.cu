@@ -237,8 +237,9 @@ static int decode_attn_impl(void *out, int64_t out_stride, const void *q, int64_
     // The ticket counters return to zero at the end of every launch.  They are
     // cleared here anyway so that a scratch buffer of unknown content works — except
     // in overlap mode, where a memset between the kernels would serialise them and
-    // the caller guarantees a zero-initialised buffer instead.
-    if (!p.overlap &&
+    // the caller guarantees a zero-initialised buffer instead, or when the caller
+    // gives that guarantee for an ordinary launch (VT_STEP_CLEAN_SCRATCH).
+    if (!p.overlap && !(flags & VT_STEP_CLEAN_SCRATCH) &&
         cudaMemsetAsync(p.fl_count, 0, static_cast<size_t>(batch) * kvh * sizeof(unsigned), s) != cudaSuccess)
       return VT_ERR_CUDA;
     // fp8 ranges with tensor maps: the tcgen05 engine where the shape allows (same schedule, same scratch)
@@ -344,7 +345,7 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
                    const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len, float scale,
                    int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
                    size_t workspace_bytes, unsigned flags, void *stream) {
-  if (batch < 0 || kvh <= 0 || (flags & ~static_cast<unsigned>(VT_STEP_OVERLAP | VT_STEP_EARLY_KV))) return VT_ERR_INVALID;
+  if (batch < 0 || kvh <= 0 || (flags & ~static_cast<unsigned>(VT_STEP_OVERLAP | VT_STEP_EARLY_KV | VT_STEP_CLEAN_SCRATCH))) return VT_ERR_INVALID;
   if (batch == 0) return VT_OK;
   if (!key || !value || !byte_off) return VT_ERR_INVALID;
   if ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(value)) & 15) return VT_ERR_INVALID;
@@ -362,7 +363,7 @@ int vt_decode_step_tma(void *out, int64_t out_stride, const void *q, int64_t q_s
                        const int32_t *seq_lens, int batch, int h, int kvh, int d, int max_seq_len, float scale,
                        int kv_dtype, const float *k_scale, const float *v_scale, float *lse, void *workspace,
                        size_t workspace_bytes, unsigned flags, const void *maps, void *stream) {
-  if (batch < 0 || kvh <= 0 || (flags & ~static_cast<unsigned>(VT_STEP_OVERLAP | VT_STEP_EARLY_KV))) return VT_ERR_INVALID;
+  if (batch < 0 || kvh <= 0 || (flags & ~static_cast<unsigned>(VT_STEP_OVERLAP | VT_STEP_EARLY_KV | VT_STEP_CLEAN_SCRATCH))) return VT_ERR_INVALID;
   if (batch == 0) return VT_OK;
   if (!maps || (reinterpret_cast<uintptr_t>(maps) & 63) != 0) return VT_ERR_INVALID;
   if (key || value) {
@@ -371,7 +372,7 @@ int vt_decode_step_tma(void *out, int64_t out_stride, const void *q, int64_t q_s
     if ((key_stride % 8) || (value_stride % 8) || key_stride < static_cast<int64_t>(kvh) * d ||
         value_stride < static_cast<int64_t>(kvh) * d)
       return VT_ERR_INVALID;
-  } else if (flags) {
+  } else if (flags & (VT_STEP_OVERLAP | VT_STEP_EARLY_KV)) {
     return VT_ERR_INVALID;   // the overlap forms are defined for the fused step only
   }
   return decode_attn_impl(out, out_stride, q, q_stride, k_table, v_table, slot_ids, seq_lens, batch, h, kvh, d,

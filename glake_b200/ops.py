@@ -240,7 +240,7 @@ def fwd_kvcache(q, k_table_ptr, v_table_ptr, max_seq_len, num_kv_heads, batch, s
 
 def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_mapping, seq_lens, max_seq_len,
                 num_kv_heads, scale, kv_cache_dtype="auto", k_scale=None, v_scale=None, lse=None, overlap=False,
-                workspace=None, maps=None):
+                workspace=None, maps=None, clean_scratch=False):
     """``reshape_and_cache`` (decode form) + ``paged_attention_v1`` in one call; one
     kernel launch for a bf16 cache.  ``key_cache`` / ``value_cache`` are the device
     addresses of the layer's pointer tables (ints), ``slot_m`` the destination byte
@@ -252,7 +252,9 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
     kernel produces: cache rows stream early, q / key / value are read after it finished.
     Pass a private zero-filled ``workspace`` (uint8 tensor) in both cases.
     ``maps`` (from :func:`decode_maps`, fp8 cache only) selects the tcgen05 kernel where
-    the head counts allow; other shapes run as without it."""
+    the head counts allow; other shapes run as without it.  ``clean_scratch=True``
+    (VT_STEP_CLEAN_SCRATCH): ``workspace`` is private, was zero-filled once and is used by
+    nothing but these calls, so the call need not clear its counters first."""
     _require_cuda(out, query, key, value, slot_m, slot_mapping, seq_lens, maps)
     batch, num_heads, head_size = query.shape
     key = key.view(batch, num_kv_heads, head_size)
@@ -261,7 +263,9 @@ def decode_step(out, query, key, value, key_cache, value_cache, slot_m, slot_map
         raise RuntimeError("decode_step(overlap=True) needs a private zero-filled workspace")
     ws = workspace if workspace is not None else attn_workspace(query.device, batch, num_heads, head_size,
                                                                 max_seq_len)
-    flags = 2 if overlap == "early_kv" else (1 if overlap else 0)
+    flags = (2 if overlap == "early_kv" else (1 if overlap else 0)) | (4 if clean_scratch else 0)
+    if clean_scratch and workspace is None:
+        raise RuntimeError("decode_step(clean_scratch=True) needs a private zero-filled workspace")
     if maps is not None:
         with torch.cuda.device(query.device):
             check(lib.vt_decode_step_tma(_ptr(out), out.stride(0), _ptr(query), query.stride(0), _ptr(key), _ptr(value),

@@ -281,9 +281,15 @@ int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype
  * before it touches q, key, value or the scratch.  It hides the launch ramp and the
  * fill of the copy ring behind the tail of the preceding kernel when that kernel
  * releases its dependents early (vt_all_reduce and vt_decode_step do); behind any
- * other kernel it behaves like an ordinary launch.  Condition (2) applies. */
+ * other kernel it behaves like an ordinary launch.  Condition (2) applies.
+ * VT_STEP_CLEAN_SCRATCH (may be combined with the others, which imply it): the caller
+ * guarantees condition (2), so the call does not clear the scratch's ticket counters first
+ * (an ordinary launch otherwise enqueues a small memset in front of the kernel: about 2 us
+ * per call).  The kernels leave the counters at zero; after a call that reported
+ * VT_ERR_KERNEL through the status word, zero the scratch again before reusing it. */
 #define VT_STEP_OVERLAP 1u
 #define VT_STEP_EARLY_KV 2u
+#define VT_STEP_CLEAN_SCRATCH 4u
 int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_stride, const void *key,
                    const void *value, int64_t key_stride, int64_t value_stride, const int64_t *byte_off,
                    const uint64_t *k_table, const uint64_t *v_table, const int64_t *slot_ids,

@@ -86,7 +86,7 @@ def test_decode_map_argument_checks():
             0.1, VT_KV_FP8_E4M3, P(A16), P(A16), None, P(A16), 1 << 20, 0]
     assert lib.vt_decode_step_tma(*args, None, None) == VT_ERR_INVALID                       # maps required
     assert lib.vt_decode_step_tma(*args, P(A16 + 8), None) == VT_ERR_INVALID                 # 64-byte aligned table
-    bad = list(args); bad[25] = 4
+    bad = list(args); bad[25] = 8
     assert lib.vt_decode_step_tma(*bad, P(A16), None) == VT_ERR_INVALID                      # unknown flag
     bad = list(args); bad[4] = None; bad[5] = None; bad[25] = 1
     assert lib.vt_decode_step_tma(*bad, P(A16), None) == VT_ERR_INVALID                      # overlap forms need the fused step
