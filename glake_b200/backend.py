@@ -23,7 +23,6 @@ import torch
 from . import ops, vmmAllocator
 from .vmm_allocator.vmm_allocator import KV_cache
 
-PHY_GRAN = vmmAllocator.granularitySize
 
 
 class nvtx_range:
@@ -57,10 +56,10 @@ class VTensorCacheEngine:
         self.device = torch.device(device)
         self.token_size = num_kv_heads * head_size * self.dtype_size
         # cache_engine.py:55-57: room for max_num_batched_tokens rows, whole chunks
-        self.max_context_size = _round_up(max_num_batched_tokens * self.token_size, PHY_GRAN)
+        self.max_context_size = _round_up(max_num_batched_tokens * self.token_size, vmmAllocator.granularitySize)
         self.kv_batch_stride = self.max_context_size
         self.vmm_kvcache_segment = []
-        cache_token_size = PHY_GRAN * cache_tokens
+        cache_token_size = vmmAllocator.granularitySize * cache_tokens
         for index in range(max_num_seqs):
             if cache_seqs > 0:
                 seg = vmmAllocator.KVcacheSegment(num_layers, self.max_context_size, cache_token_size,

@@ -25,7 +25,7 @@ from dataclasses import dataclass
 from enum import Enum
 from typing import Dict, List, Optional
 
-PHY_GRAN = 2 * 1024 * 1024
+PHY_GRAN = 2 * 1024 * 1024       # bytes of a physical chunk; vmmAllocator.set_chunk_bytes keeps it in step
 PREFILL_HEADROOM_TOKENS = 100   # sequence.py:343: a prompt reserves room for 100 more tokens
 
 

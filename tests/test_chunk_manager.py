@@ -51,11 +51,17 @@ def test_admission_watermark_and_cached_slots():
     assert m.can_allocate(c) == cm.AllocStatus.OK and m.allocate(c) and c.slot == 0
 
 
-def test_manager_drives_the_allocator_consistently():
+@pytest.mark.parametrize("chunk_mib", [2, 8])
+def test_manager_drives_the_allocator_consistently(chunk_mib):
     """A random serving trace: the manager books chunks, the allocator maps them.
     At every step the allocator holds no more than the manager booked, nothing
-    the kernels need is unmapped, and budgets are conserved."""
+    the kernels need is unmapped, and budgets are conserved.  Also with 8 MiB
+    chunks (vmmAllocator.set_chunk_bytes): a growth costs the driver the same per
+    chunk whatever its size, so larger chunks are a tuning the accounting must follow."""
     from glake_b200 import vmmAllocator as A
+    A.set_chunk_bytes(chunk_mib * MiB)
+    CH = A.granularitySize
+    assert cm.PHY_GRAN == CH
     layers, kvh, max_seqs = 3, 8, 6
     row = kvh * 128 * 2                         # 2 KiB -> 1024 rows per chunk
     handles = 60                                # per layer
@@ -119,3 +125,4 @@ def test_manager_drives_the_allocator_consistently():
     finally:
         A.shutdown()
         lib.vt_use_mock_driver(0)
+        A.set_chunk_bytes(2 * MiB)
