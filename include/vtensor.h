@@ -86,7 +86,10 @@ int vt_mock_map_delay_us(int us);
 /* Creates n_chunks physical chunks of chunk_bytes (0 = 2 MiB; must be a multiple
  * of the device's allocation granularity) on `device` and starts the background
  * growth worker.  Replaces init_physical_handle (vmm_allocator.cpp:113-151) and
- * PhyBlock (vmm_allocator.cpp:154-174). */
+ * PhyBlock (vmm_allocator.cpp:154-174).  The driver charges per chunk, not per byte
+ * (B200: cuMemCreate 0.07 ms, cuMemSetAccess 0.15 ms per chunk of 2 to 32 MiB), so a
+ * larger chunk makes pool creation and every growth cheaper per byte at the price of
+ * up to one chunk of unused memory per range. */
 int vt_pool_create(int device, size_t n_chunks, size_t chunk_bytes, vt_pool **out);
 /* Stops the worker, releases every chunk.  All segments and tables of the pool
  * must have been destroyed first (VT_ERR_STATE otherwise). */
