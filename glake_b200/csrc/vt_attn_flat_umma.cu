@@ -77,10 +77,11 @@ constexpr int kOffMisc = kOffFac + 4 * 32 * 4;        // tmem slot, failed, merg
 constexpr int kOffMeta = kOffMisc + 16;               // prefix[batch + 1], lens[batch]
 __host__ __device__ constexpr int umma_smem_bytes(int batch) { return 1024 + kOffMeta + (2 * batch + 2) * 4; }
 
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *map, int x, int y, int z, uint32_t bar) {
+// Tensor copy with an L2 eviction-priority hint (KV rows are streamed once per step).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *map, int x, int y, int z, uint32_t bar, uint64_t policy) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar)
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4}], [%5], %6;"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(z), "r"(bar), "l"(policy)
       : "memory");
 }
 // A warp reads 16 consecutive columns of its 32 lanes (thread i <- lane base + i).
@@ -229,6 +230,7 @@ __global__ void __launch_bounds__(kUThreads, 1) attn_flat_umma_f8_kernel(AttnPar
     // lanes 0-7 fetch kv heads 0-7 of the slab; all 32 lanes patch a stream's last tile.
     const int kv = warp - kUCWarps;
     const uint32_t full = kv ? v_full : k_full, empty = kv ? v_empty : k_empty, aux = kv ? aux_v : aux_k;
+    const uint64_t policy = l2_policy_evict_first();
     bool ok = true;
     int it = 0;
     uint32_t aux_n = 0;
@@ -251,7 +253,7 @@ __global__ void __launch_bounds__(kUThreads, 1) attn_flat_umma_f8_kernel(AttnPar
         const uint32_t stage = ring_s + s * kUStageB + kv * kKVTileB;
         if (lane == 0) mbar_arrive_expect_tx(bar, kKVTileB);
         __syncwarp();
-        if (lane < 8) tma_load_3d(stage + lane * kHeadTileB, map, 0, head, t0, bar);
+        if (lane < 8) tma_load_3d(stage + lane * kHeadTileB, map, 0, head, t0, bar, policy);
         if (!patch) continue;
         if (!mbar_wait(aux, aux_n & 1)) { ok = false; break; }
         ++aux_n;
