@@ -311,6 +311,15 @@ class DecodeRunner:
             # >= 1 MiB per host->device copy and >= 4 layers per group: every group boundary is a
             # cross-stream dependency that interrupts the layer-to-layer overlap of the kernels
             self.io_group = max(1, min(layers, max(4, -(-(1 << 20) // per_layer))))
+            # Only the first host->device copy and the last device->host copy of a step are exposed
+            # (everything between hides behind the kernels), so the first input group and the last
+            # output group are a single layer; the groups between have io_group layers.
+            g = self.io_group
+            self.in_groups = [(0, 1)] + [(l, min(l + g, layers)) for l in range(1, layers, g)]
+            body = max(layers - 1, 0)
+            self.out_groups = [(l, min(l + g, body)) for l in range(0, body, g)] + [(layers - 1, layers)]
+            self.in_starts = {a for a, _ in self.in_groups}
+            self.out_ends = {b - 1: a for a, b in self.out_groups}
 
     def _body(self, meta):
         """Everything the device does in one step after the per-step integers have
@@ -324,18 +333,17 @@ class DecodeRunner:
             # the PCIe time hides behind the attention kernels instead of bracketing them.
             self.s_in.wait_stream(main)
             self.s_out.wait_stream(main)
-            grp = self.io_group   # layers per copy, so that every transfer is worth a DMA launch
             with torch.cuda.stream(self.s_in):
-                for l0 in range(0, n_layers, grp):
-                    self.q[l0:l0 + grp].copy_(self.hq[l0:l0 + grp], non_blocking=True)
-                    self.k[l0:l0 + grp].copy_(self.hk[l0:l0 + grp], non_blocking=True)
-                    self.v[l0:l0 + grp].copy_(self.hv[l0:l0 + grp], non_blocking=True)
+                for l0, l1 in self.in_groups:     # several layers per copy, so that a transfer is worth a DMA launch
+                    self.q[l0:l1].copy_(self.hq[l0:l1], non_blocking=True)
+                    self.k[l0:l1].copy_(self.hk[l0:l1], non_blocking=True)
+                    self.v[l0:l1].copy_(self.hv[l0:l1], non_blocking=True)
                     self.ev_in[l0].record(self.s_in)
         for layer in range(n_layers):
             kc, vc = self.engine.gpu_cache[layer]
             ks = self.k_scale[layer] if self.k_scale is not None else None
             vs = self.v_scale[layer] if self.v_scale is not None else None
-            if self.host_io and layer % self.io_group == 0:
+            if self.host_io and layer in self.in_starts:
                 main.wait_event(self.ev_in[layer])
             torch.cuda.nvtx.range_push(f"layer {layer}: append + attention")
             ops.decode_step(self.out[layer].view(b, self.impl.num_heads, self.impl.head_size),
@@ -347,8 +355,8 @@ class DecodeRunner:
             torch.cuda.nvtx.range_pop()
             if self.post_layer is not None:
                 self.post_layer(layer)
-            if self.host_io and ((layer + 1) % self.io_group == 0 or layer == n_layers - 1):
-                l0 = layer - layer % self.io_group
+            if self.host_io and layer in self.out_ends:
+                l0 = self.out_ends[layer]
                 self.ev_out[layer].record(main)
                 self.s_out.wait_event(self.ev_out[layer])
                 with torch.cuda.stream(self.s_out):
