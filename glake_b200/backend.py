@@ -307,17 +307,21 @@ class DecodeRunner:
             self.s_in, self.s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
             self.ev_in = [torch.cuda.Event() for _ in range(layers)]
             self.ev_out = [torch.cuda.Event() for _ in range(layers)]
-            per_layer = batch * (hd + 2 * kd) * 2
-            # >= 1 MiB per host->device copy and >= 4 layers per group: every group boundary is a
-            # cross-stream dependency that interrupts the layer-to-layer overlap of the kernels
-            self.io_group = max(1, min(layers, max(4, -(-(1 << 20) // per_layer))))
-            # Only the first host->device copy and the last device->host copy of a step are exposed
-            # (everything between hides behind the kernels), so the first input group and the last
-            # output group are a single layer; the groups between have io_group layers.
-            g = self.io_group
-            self.in_groups = [(0, 1)] + [(l, min(l + g, layers)) for l in range(1, layers, g)]
-            body = max(layers - 1, 0)
-            self.out_groups = [(l, min(l + g, body)) for l in range(0, body, g)] + [(layers - 1, layers)]
+            # Layers per copy.  Only the first host->device copy and the last device->host copy of a step
+            # are exposed (the others hide behind the kernels), and every group boundary is a cross-stream
+            # dependency that interrupts the layer-to-layer overlap of the kernels: the input groups
+            # therefore double from one layer up to 16 (each copy is in flight while the group before it
+            # computes, which takes 8.4 GB/s of PCIe for the 7B shape), the output groups mirror them.
+            sizes, left, n = [], layers, 1
+            while left > 0:
+                sizes.append(min(n, left))
+                left -= sizes[-1]
+                n = min(2 * n, 16)
+            self.io_group = max(sizes)
+            starts = [sum(sizes[:i]) for i in range(len(sizes))]
+            self.in_groups = [(a, a + n) for a, n in zip(starts, sizes)]
+            rstarts = [sum(sizes[::-1][:i]) for i in range(len(sizes))]
+            self.out_groups = [(a, a + n) for a, n in zip(rstarts, sizes[::-1])]
             self.in_starts = {a for a, _ in self.in_groups}
             self.out_ends = {b - 1: a for a, b in self.out_groups}
 
