@@ -646,6 +646,7 @@ def growth_record_large_chunks(name, seed, steps, chunk_mib):
             finally:
                 job.close()
         finally:
+            A.shutdown()              # no-op after job.close(); releases the pool if the job never came up
             A.set_chunk_bytes(2 << 20)
     except Exception as exc:      # an extra must not take the bench line down
         return {"error": f"{type(exc).__name__}: {exc}"[:300]}
