@@ -260,10 +260,11 @@ int vt_decode_attn_plan(int batch, int h, int kvh, int max_seq_len, int kv_dtype
  * (vt_append with max_seq_len == 1) and attend (vt_decode_attn).  Results are
  * identical to the two calls in sequence; seq_lens INCLUDES the appended token and
  * byte_off[i] is its destination offset, as extend_kv_cache_batch returned it.
- * With bf16 KV the two are ONE kernel launch: the attention kernel reads the
- * newest row from key / value directly and stores it into the range itself, so
- * the step has no append launch and no dependency between the two.  Otherwise the
- * call enqueues the append kernel followed by the attention kernels.
+ * On the persistent schedule (every supported head shape of both cache types) the
+ * two are ONE kernel launch: the attention kernel takes the newest row from key /
+ * value (copied for a bf16 cache, quantised for an fp8 cache) and stores it into the
+ * range itself, so the step has no append launch and no dependency between the two.
+ * Otherwise the call enqueues the append kernel followed by the attention kernels.
  * Replaces the pair of calls in XFormersImpl.forward
  * (vllm/attention/backends/xformers.py:310-312 and :407-430).
  * key / value must be 16-byte aligned with strides that are multiples of 8 elements.
@@ -307,8 +308,8 @@ int vt_decode_step(void *out, int64_t out_stride, const void *q, int64_t q_strid
  *   maps   device copy of the table vt_decode_maps_encode filled: for every slot id a
  *          K and a V tensor map of this layer's ranges (2 x 128 bytes per slot,
  *          64-byte aligned).
- * key / value may both be NULL (plain attention over rows already appended; flags
- * must then be 0).  Shapes the tcgen05 kernel does not take (kv heads not a power of
+ * key / value may both be NULL (plain attention over rows already appended; of the
+ * flags only VT_STEP_CLEAN_SCRATCH applies then).  Shapes the tcgen05 kernel does not take (kv heads not a power of
  * two >= 8, more than 4 q heads per kv head, bf16 ranges) run exactly as vt_decode_step.
  * vt_decode_maps_encode writes the table into HOST memory (n_slots x 256 bytes, 64-byte
  * aligned; the caller copies it to the device once): k_bases / v_bases are the slots'
